@@ -13,7 +13,7 @@ __version__ = "0.1.0"
 _LAZY = {
     "Engine": "engine", "GenerationParams": "engine", "GenerationOutput": "engine", "KvCacheOptions": "engine",
     "PagedSchedulerConfig": "engine", "FinishReason": "engine", "RequestStatus": "engine", "ModelRunner": "engine",
-    "StepEntry": "engine", "SamplingParams": "sampling", "Qwen3Config": "config", "LegelixConfig": "config", "GefovikConfig": "config", "load_model_config": "config",
+    "StepEntry": "engine", "SamplingParams": "sampling", "Qwen3Config": "config", "LegelixConfig": "config", "GefovikConfig": "config", "FekotarConfig": "config", "load_model_config": "config",
     "register_architecture": "config", "write_random_model": "weights",
 }
 

@@ -1,6 +1,7 @@
 """Typed configurations, the architecture registry, and the architecture-neutral model spec."""
 
 from .errors import ConfigError, InvalidArgumentError, OutOfPagesError, WeightError, ZephyrError
+from .fekotar import FekotarConfig
 from .gefovik import GefovikConfig
 from .legelix import LegelixConfig
 from .qwen3 import Qwen3Config
@@ -11,7 +12,7 @@ from .spec import (FeedForwardSpec, InputSpec, LayerCall, LayerSpec, MixerSpec, 
                    PositionSpec)
 
 __all__ = [
-    "ArchitectureEntry", "ConfigError", "GefovikConfig", "FeedForwardSpec", "InputSpec", "InvalidArgumentError", "LayerCall", "LayerSpec", "LegelixConfig",
+    "ArchitectureEntry", "ConfigError", "FekotarConfig", "GefovikConfig", "FeedForwardSpec", "InputSpec", "InvalidArgumentError", "LayerCall", "LayerSpec", "LegelixConfig",
     "MixerSpec", "ModelSpec", "NormSpec", "OutOfPagesError", "OutputSpec", "PositionSpec", "Qwen3Config", "WeightError",
     "ZephyrError", "load_model_config", "load_model_spec", "read_config_json", "register_architecture",
     "registered_architectures", "resolve_architecture", "unregister_architecture",

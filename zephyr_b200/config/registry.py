@@ -16,6 +16,7 @@ from pathlib import Path
 from typing import Any, Mapping
 
 from .errors import ConfigError
+from .fekotar import FekotarConfig
 from .gefovik import GefovikConfig
 from .legelix import LegelixConfig
 from .qwen3 import Qwen3Config
@@ -109,3 +110,4 @@ def load_model_spec(model_dir: str | Path) -> ModelSpec:
 register_architecture(Qwen3Config.model_type, Qwen3Config.architecture, Qwen3Config)
 register_architecture(LegelixConfig.model_type, LegelixConfig.architecture, LegelixConfig)
 register_architecture(GefovikConfig.model_type, GefovikConfig.architecture, GefovikConfig)
+register_architecture(FekotarConfig.model_type, FekotarConfig.architecture, FekotarConfig)

@@ -27,34 +27,96 @@ constexpr int ROUTE_PER_LANE = 8;      // up to 256 router outputs
 constexpr int ROUTE_WARPS = 4;
 
 // ---------------------------------------------------------------------------------------------- route
+// Further forms, each a parameter: scores that are the logistic function of each logit on its own
+// (`sigmoid_scores`) instead of a softmax over all; a choice limited to groups (the outputs form `groups`
+// equal runs of neighbours; a group's mark is the sum of its `group_top` largest choice values, and only
+// outputs of the `keep` groups with the largest marks can be taken; ties: the lower group); and a
+// multiplier on the weights (`weight_scale`).
+constexpr int ROUTE_GROUP_TOP_MAX = 4;
+
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 route_kernel(int* ids, float* weights, const float* logits, long long logits_stride, const float* correction,
-             int tokens, int outputs, int top) {
-  const int t = blockIdx.x * ROUTE_WARPS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+             int tokens, int outputs, int top, int sigmoid_scores, int groups, int keep, int group_top,
+             float weight_scale) {
+  __shared__ float choice_of[ROUTE_WARPS][32 * ROUTE_PER_LANE];
+  __shared__ float mark_of[ROUTE_WARPS][32 * ROUTE_PER_LANE];
+  const int warp = threadIdx.x >> 5;
+  const int t = blockIdx.x * ROUTE_WARPS + warp, lane = threadIdx.x & 31;
   if (t >= tokens) return;
   const float* z = logits + t * logits_stride;
   float s[ROUTE_PER_LANE], c[ROUTE_PER_LANE];
-  float top_z = -INFINITY;
+  if (sigmoid_scores) {
 #pragma unroll
-  for (int i = 0; i < ROUTE_PER_LANE; ++i) {
-    const int e = lane + 32 * i;
-    s[i] = e < outputs ? z[e] : -INFINITY;
-    top_z = fmaxf(top_z, s[i]);
+    for (int i = 0; i < ROUTE_PER_LANE; ++i) {
+      const int e = lane + 32 * i;
+      s[i] = e < outputs ? 1.0f / (1.0f + expf(-z[e])) : 0.0f;
+    }
+  } else {
+    float top_z = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < ROUTE_PER_LANE; ++i) {
+      const int e = lane + 32 * i;
+      s[i] = e < outputs ? z[e] : -INFINITY;
+      top_z = fmaxf(top_z, s[i]);
+    }
+    top_z = warp_max(top_z);
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < ROUTE_PER_LANE; ++i) {
+      const int e = lane + 32 * i;
+      s[i] = e < outputs ? expf(s[i] - top_z) : 0.0f;
+      sum += s[i];
+    }
+    sum = warp_sum(sum);
+#pragma unroll
+    for (int i = 0; i < ROUTE_PER_LANE; ++i) s[i] = s[i] / sum;
   }
-  top_z = warp_max(top_z);
-  float sum = 0.0f;
 #pragma unroll
   for (int i = 0; i < ROUTE_PER_LANE; ++i) {
     const int e = lane + 32 * i;
-    s[i] = e < outputs ? expf(s[i] - top_z) : 0.0f;
-    sum += s[i];
-  }
-  sum = warp_sum(sum);
-#pragma unroll
-  for (int i = 0; i < ROUTE_PER_LANE; ++i) {
-    const int e = lane + 32 * i;
-    s[i] = s[i] / sum;
     c[i] = e < outputs ? s[i] + (correction != nullptr ? correction[e] : 0.0f) : -INFINITY;
+  }
+  if (groups > 1 && keep < groups) {
+    const int members = outputs / groups;
+#pragma unroll
+    for (int i = 0; i < ROUTE_PER_LANE; ++i)
+      if (lane + 32 * i < outputs) choice_of[warp][lane + 32 * i] = c[i];
+    __syncwarp();
+    for (int g = lane; g < groups; g += 32) {
+      // The group's largest `group_top` values, by repeated search (the groups are small).
+      int taken[ROUTE_GROUP_TOP_MAX];
+      float mark = 0.0f;
+      for (int k = 0; k < group_top && k < members; ++k) {
+        float best = -INFINITY;
+        int best_m = -1;
+        for (int m = 0; m < members; ++m) {
+          bool used = false;
+          for (int j = 0; j < k; ++j) used = used || taken[j] == m;
+          const float v = choice_of[warp][g * members + m];
+          if (!used && (best_m < 0 || v > best)) {
+            best = v;
+            best_m = m;
+          }
+        }
+        taken[k] = best_m;
+        mark += best;
+      }
+      mark_of[warp][g] = mark;
+    }
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < ROUTE_PER_LANE; ++i) {
+      const int e = lane + 32 * i;
+      if (e >= outputs) continue;
+      const int g = e / members;
+      const float mine = mark_of[warp][g];
+      int ahead = 0;
+      for (int o = 0; o < groups; ++o) {
+        const float other = mark_of[warp][o];
+        ahead += (other > mine || (other == mine && o < g)) ? 1 : 0;
+      }
+      if (ahead >= keep) c[i] = -INFINITY;
+    }
   }
   for (int j = 0; j < top; ++j) {
     // The largest remaining choice; among equals the lowest index.
@@ -87,7 +149,7 @@ route_kernel(int* ids, float* weights, const float* logits, long long logits_str
     w = __shfl_sync(0xffffffffu, w, best_e & 31);
     if (lane == 0) {
       ids[static_cast<size_t>(t) * top + j] = best_e;
-      weights[static_cast<size_t>(t) * top + j] = w;
+      weights[static_cast<size_t>(t) * top + j] = w * weight_scale;
     }
   }
 }
@@ -395,14 +457,28 @@ using namespace zb;
 ZB_API int zb_route_max_outputs() { return 32 * ROUTE_PER_LANE; }
 ZB_API int zb_expert_tile_rows(int dtype) { return dtype == DTYPE_F32 ? TP_BM : TM_BM; }
 
-ZB_API int zb_route(int* ids, float* weights, const float* logits, long long logits_stride, const float* correction,
-                    int tokens, int outputs, int top, void* stream) {
+// sigmoid_scores: 0 softmax over all outputs, 1 the logistic function of each.  groups <= 1: no limit on the
+// choice; else the outputs form `groups` equal runs and only the `keep` best runs (by the sum of their
+// `group_top` largest choice values) can be taken from: keep * (outputs / groups) must reach `top`.
+ZB_API int zb_route_grouped(int* ids, float* weights, const float* logits, long long logits_stride,
+                            const float* correction, int tokens, int outputs, int top, int sigmoid_scores, int groups,
+                            int keep, int group_top, float weight_scale, void* stream) {
   if (tokens < 0 || outputs <= 0 || top <= 0 || top > outputs) return ERR_BAD_ARGUMENT;
-  if (outputs > 32 * ROUTE_PER_LANE) return ERR_UNSUPPORTED;
+  if (groups > 1 && (outputs % groups != 0 || keep <= 0 || keep > groups || group_top <= 0 ||
+                     keep * (outputs / groups) < top))
+    return ERR_BAD_ARGUMENT;
+  if (outputs > 32 * ROUTE_PER_LANE || (groups > 1 && group_top > ROUTE_GROUP_TOP_MAX)) return ERR_UNSUPPORTED;
   if (tokens == 0) return OK;
   route_kernel<<<(tokens + ROUTE_WARPS - 1) / ROUTE_WARPS, ROUTE_WARPS * 32, 0, static_cast<cudaStream_t>(stream)>>>(
-      ids, weights, logits, logits_stride, correction, tokens, outputs, top);
+      ids, weights, logits, logits_stride, correction, tokens, outputs, top, sigmoid_scores, groups, keep, group_top,
+      weight_scale);
   return launch_result();
+}
+
+ZB_API int zb_route(int* ids, float* weights, const float* logits, long long logits_stride, const float* correction,
+                    int tokens, int outputs, int top, void* stream) {
+  return zb_route_grouped(ids, weights, logits, logits_stride, correction, tokens, outputs, top, 0, 1, 1, 1, 1.0f,
+                          stream);
 }
 
 ZB_API int zb_route_align(int* plan, int* slots, int* place_of_slot, const int* ids, int num_slots, int experts,

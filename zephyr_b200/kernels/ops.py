@@ -57,6 +57,22 @@ _SIGNATURES = {
     "zb_act_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "zb_head_linear": [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_longlong, c_longlong, c_int, c_int, c_int,
                        c_int, c_int, c_int, c_int, c_void_p],
+    "zb_head_linear_strided": [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_longlong, c_longlong, c_int, c_int,
+                               c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "zb_route_grouped": [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                         c_int, c_float, c_void_p],
+    "zb_pair_embedding": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                          c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int, c_int, c_int, c_void_p,
+                          c_void_p],
+    "zb_store_last_token": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "zb_sum_rms_norm": [c_void_p, c_longlong, c_int, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_void_p,
+                        c_int, c_float, c_int, c_int, c_void_p],
+    "zb_clamped_gate": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_float, c_float,
+                        c_void_p],
+    "zb_scale_rows": [c_void_p, c_longlong, c_float, c_void_p],
+    "zb_latent_rope": [c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_longlong, c_void_p, c_float, c_void_p,
+                       c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                       c_int, c_int, c_void_p, c_void_p],
     "zb_route_max_outputs": [],
     "zb_expert_tile_rows": [c_int],
     "zb_route": [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p],
@@ -434,6 +450,120 @@ def embedding_f32(table: torch.Tensor, ids: torch.Tensor, status: torch.Tensor, 
     _check(library().zb_embedding_f32(_ptr(out), _ptr(copy), _ptr(table), _ptr(ids), float(scale), ids.numel(), H, V,
                                       DTYPE_CODE[table.dtype], _ptr(status), _stream()), "embedding_f32")
     return (out, copy) if rounded else out
+
+
+def pair_embedding(table: torch.Tensor, pair_table: torch.Tensor, ctx_ids: torch.Tensor, positions: torch.Tensor,
+                   token_row: torch.Tensor, row_q_start: torch.Tensor, row_q_len: torch.Tensor,
+                   state_slots: torch.Tensor, last_token: torch.Tensor, mul_prev: int, mul_cur: int,
+                   status: torch.Tensor, rounded: bool = False):
+    """Rows of ``table`` plus rows of ``pair_table`` ([buckets + 1, H]) chosen by a hash of the token and the
+    token before it, (prev * mul_prev + id * mul_cur) mod buckets, as a float32 stream [T, H]; a sequence's
+    first token (position 0) takes the pair table's last row.  The token before a row's first new token is
+    ``last_token[state_slots[row]]`` (int32 [slots]); after the lookup the slots take the rows' last new
+    tokens.  With ``rounded`` returns (float32 rows, the same rows in the tables' type)."""
+    _cuda(table, pair_table, ctx_ids, positions, token_row, row_q_start, row_q_len, state_slots, last_token, status)
+    _i32(ctx_ids, positions, token_row, row_q_start, row_q_len, state_slots, last_token)
+    _require(table.dim() == 2 and table.is_contiguous() and table.dtype in DTYPE_CODE and pair_table.dim() == 2
+             and pair_table.is_contiguous() and pair_table.dtype == table.dtype and pair_table.shape[1] == table.shape[1]
+             and pair_table.shape[0] >= 2, "table [V, H] and pair table [buckets + 1, H] of one type")
+    _require(last_token.is_contiguous() and positions.numel() == ctx_ids.numel() == token_row.numel()
+             and row_q_start.numel() == row_q_len.numel() == state_slots.numel(), "one position and row per token")
+    V, H = table.shape
+    T, R = ctx_ids.numel(), row_q_start.numel()
+    out = torch.empty((T, H), dtype=torch.float32, device=table.device)
+    copy = torch.empty((T, H), dtype=table.dtype, device=table.device) if rounded else None
+    lib = library()
+    _check(lib.zb_pair_embedding(_ptr(out), _ptr(copy), _ptr(table), _ptr(pair_table), _ptr(ctx_ids), _ptr(positions),
+                                 _ptr(token_row), _ptr(row_q_start), _ptr(state_slots), _ptr(last_token), T, H, V,
+                                 pair_table.shape[0] - 1, int(mul_prev), int(mul_cur), R, last_token.numel(),
+                                 DTYPE_CODE[table.dtype], _ptr(status), _stream()), "pair_embedding")
+    _check(lib.zb_store_last_token(_ptr(last_token), _ptr(ctx_ids), _ptr(row_q_start), _ptr(row_q_len),
+                                   _ptr(state_slots), R, last_token.numel(), _stream()), "store_last_token")
+    return (out, copy) if rounded else out
+
+
+def sum_rms_norm(x: torch.Tensor, a: torch.Tensor | None, b: torch.Tensor | None, w: torch.Tensor | None,
+                 eps: float, out_dtype: torch.dtype | None = None) -> torch.Tensor | None:
+    """x (float32 [rows, H], unit inner stride, rows may be slices of wider rows) += (a + b) in place, where a
+    and b are contiguous [rows, H] summands of either type or None; then, with a scale ``w``, returns
+    x / sqrt(mean(x^2) + eps) * w in ``out_dtype``.  Statistics and sums are float32."""
+    _cuda(x, a, b, w)
+    _require(x.dim() == 2 and x.dtype == torch.float32 and x.stride(1) == 1, "a float32 stream [rows, H]")
+    rows, H = x.shape
+    for summand in (a, b):
+        _require(summand is None or (summand.shape == x.shape and summand.is_contiguous() and summand.dtype in DTYPE_CODE),
+                 "summands are contiguous [rows, H]")
+    out = None
+    if w is not None:
+        out = torch.empty((rows, H), dtype=out_dtype or torch.float32, device=x.device)
+    _check(library().zb_sum_rms_norm(_ptr(out), H, DTYPE_CODE[out.dtype] if out is not None else 0, _ptr(x), x.stride(0),
+                                     _ptr(a), DTYPE_CODE[a.dtype] if a is not None else 0, _ptr(b),
+                                     DTYPE_CODE[b.dtype] if b is not None else 0, _ptr(w),
+                                     _scale_code(w, H) if w is not None else 0, float(eps), rows, H, _stream()),
+           "sum_rms_norm")
+    return out
+
+
+def clamped_gate(gate_up: torch.Tensor, bias: torch.Tensor | None, limit: float, alpha: float, shift: float,
+                 out_dtype: torch.dtype, blocked: bool = False) -> torch.Tensor:
+    """g * sigmoid(alpha * g) * (u + shift) with g = min(G + b_g, limit) and u = clamp(U + b_u, -limit, limit),
+    for a contiguous product [T, 2I] (float32 or bfloat16) that holds G then U, or with ``blocked`` blocks
+    of 8 gate columns each followed by its 8 up columns; ``bias`` float32 [2I] in the same column order, or
+    None.  Returns [T, I] in ``out_dtype``."""
+    _cuda(gate_up, bias)
+    _require(gate_up.dim() == 2 and gate_up.is_contiguous() and gate_up.dtype in DTYPE_CODE and gate_up.shape[1] % 2 == 0,
+             "gate_up must be a contiguous [T, 2I] tensor")
+    T, two_i = gate_up.shape
+    _f32_vector(bias, two_i, "the bias")
+    out = torch.empty((T, two_i // 2), dtype=out_dtype, device=gate_up.device)
+    _check(library().zb_clamped_gate(_ptr(out), DTYPE_CODE[out_dtype], _ptr(gate_up), DTYPE_CODE[gate_up.dtype], _ptr(bias),
+                                     T, two_i // 2, int(blocked), float(limit), float(alpha), float(shift), _stream()),
+           "clamped_gate")
+    return out
+
+
+def scale_rows(y: torch.Tensor, scale: float) -> torch.Tensor:
+    """y *= scale in place, for a contiguous float32 tensor."""
+    _cuda(y)
+    _require(y.dtype == torch.float32 and y.is_contiguous(), "a contiguous float32 tensor")
+    _check(library().zb_scale_rows(_ptr(y), y.numel(), float(scale), _stream()), "scale_rows")
+    return y
+
+
+def latent_rope(q: torch.Tensor | None, nh: int, q_head_stride: int, q_rot_offset: int, q_out: torch.Tensor | None,
+                kv: torch.Tensor | None, rank: int, rot: int, norm_w: torch.Tensor | None, eps: float,
+                freqs: torch.Tensor | None, mult: float, positions: torch.Tensor, token_row: torch.Tensor,
+                kv_cache: torch.Tensor | None, block_table: torch.Tensor, status: torch.Tensor,
+                dtype: torch.dtype) -> None:
+    """What latent attention with a rotated part keeps of a position, and the rotated part of its queries.
+    ``kv`` (float32 [T, >= rank + rot], unit inner stride): the first ``rank`` values are RMS-normed with
+    ``norm_w`` and the last ``rot`` rotated by the position's angles; the row of rank + rot values goes into
+    the keys-only pages of ``kv_cache``.  ``q`` (float32, heads ``q_head_stride`` apart, the rotated part at
+    ``q_rot_offset`` of a head): rotated the same way into the last ``rot`` values of every head of
+    ``q_out`` [T, nh * (rank + rot)].  Rotation of halves: value i pairs with value i + rot / 2; angle =
+    position * freqs[i] in float32; cosine and sine are multiplied by ``mult``."""
+    _cuda(q, q_out, kv, norm_w, freqs, positions, token_row, kv_cache, block_table, status)
+    _i32(positions, token_row, block_table)
+    T = positions.numel()
+    width = rank + rot
+    for vector, size in ((norm_w, rank), (freqs, rot // 2)):
+        _require(vector is None or (vector.dtype == torch.float32 and vector.is_contiguous() and vector.numel() == size),
+                 f"a float32 vector of {size} values")
+    if nh > 0:
+        _require(q is not None and q.dtype == torch.float32 and q.dim() == 2 and q.stride(1) == 1 and q.shape[0] == T
+                 and q.shape[1] >= (nh - 1) * q_head_stride + q_rot_offset + rot, "float32 queries [T, heads * head stride]")
+        _require(q_out is not None and q_out.is_contiguous() and q_out.shape == (T, nh * width) and q_out.dtype == dtype,
+                 "q_out [T, heads * (rank + rot)] in the model's type")
+    pages, page_size = (0, 1)
+    if kv_cache is not None:
+        _require(kv is not None and kv.dtype == torch.float32 and kv.dim() == 2 and kv.stride(1) == 1
+                 and kv.shape[0] == T and kv.shape[1] >= width, "float32 latent rows [T, rank + rot]")
+        pages, page_size = _cache_geometry(kv_cache, 1, width, 0, dtype)
+    _check(library().zb_latent_rope(
+        _ptr(q_out), _ptr(q), q.stride(0) if q is not None else 0, int(q_head_stride), int(q_rot_offset), _ptr(kv),
+        kv.stride(0) if kv is not None else 0, _ptr(norm_w), float(eps), _ptr(freqs), float(mult), _ptr(positions),
+        _ptr(token_row), _ptr(kv_cache), _ptr(block_table), block_table.shape[1], page_size, pages, block_table.shape[0],
+        T, int(nh), int(rank), int(rot), DTYPE_CODE[dtype], _ptr(status), _stream()), "latent_rope")
 
 
 CONV_MAX_TAPS = 8
@@ -1235,23 +1365,38 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = Non
 
 # ------------------------------------------------------------- products per head and per expert
 def head_linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None,
-                gate: torch.Tensor | None = None) -> torch.Tensor:
+                gate: torch.Tensor | None = None, x_head_stride: int | None = None,
+                out: torch.Tensor | None = None, out_head_stride: int | None = None) -> torch.Tensor:
     """y[t, h, :] = w[h] x[t, h, :] for x [T, heads * K] (unit inner stride) and w [heads, N, K]: a product
     that is block-diagonal over heads; returns [T, heads * N] in ``out_dtype`` (default: w's type).  x may be
-    float32 beside bfloat16 matrices.  ``gate`` (float32 [T, >= heads], unit inner stride): head h's output
-    is multiplied by sigmoid(gate[t, h]).  float32 sums in the order of k."""
-    _cuda(x, w, gate)
+    float32 beside bfloat16 matrices.  ``gate`` (float32, unit inner stride): [T, >= heads] multiplies head
+    h's output by sigmoid(gate[t, h]); [T, heads * N] multiplies every output value by the logistic function
+    of its own gate value.  float32 sums in the order of k.
+
+    ``x_head_stride``: head h's K inputs start at x[t, h * x_head_stride] (heads that are slices of wider
+    ones; x is then [T, >= heads * x_head_stride]).  ``out`` with ``out_head_stride``: head h's N outputs go
+    to out[t, h * out_head_stride ...] of a given [T, heads * out_head_stride] tensor, the rest of which is
+    left as it is."""
+    _cuda(x, w, gate, out)
     heads, N, K = w.shape
-    _require(x.dim() == 2 and x.shape[1] == heads * K and x.stride(1) == 1 and w.is_contiguous()
-             and x.dtype in (w.dtype, torch.float32) and w.dtype in DTYPE_CODE,
+    xhs = K if x_head_stride is None else int(x_head_stride)
+    _require(x.dim() == 2 and xhs >= K and x.shape[1] >= (heads - 1) * xhs + K and x.stride(1) == 1
+             and w.is_contiguous() and x.dtype in (w.dtype, torch.float32) and w.dtype in DTYPE_CODE,
              "x [T, heads * K] in w's type or float32, and w [heads, N, K]")
+    per_element = gate is not None and gate.shape[1] == heads * N and N > 1
     _require(gate is None or (gate.dtype == torch.float32 and gate.dim() == 2 and gate.shape[0] == x.shape[0]
-                              and gate.shape[1] >= heads and gate.stride(1) == 1), "one float32 gate per token and head")
-    out = torch.empty((x.shape[0], heads * N), dtype=out_dtype or w.dtype, device=x.device)
-    _check(library().zb_head_linear(_ptr(out), _ptr(x), _ptr(w), _ptr(gate), x.stride(0), out.stride(0),
-                                    gate.stride(0) if gate is not None else 0, x.shape[0], heads, N, K,
-                                    DTYPE_CODE[x.dtype], DTYPE_CODE[w.dtype], DTYPE_CODE[out.dtype], _stream()),
-           "head_linear")
+                              and gate.shape[1] >= heads and gate.stride(1) == 1),
+             "one float32 gate per token and head, or per token and output value")
+    yhs = N if out_head_stride is None else int(out_head_stride)
+    if out is None:
+        _require(yhs == N, "a head stride of the output needs the output tensor")
+        out = torch.empty((x.shape[0], heads * N), dtype=out_dtype or w.dtype, device=x.device)
+    _require(out.dim() == 2 and out.shape[0] == x.shape[0] and out.stride(1) == 1 and yhs >= N
+             and out.shape[1] >= (heads - 1) * yhs + N and out.dtype in DTYPE_CODE, "out [T, heads * out_head_stride]")
+    _check(library().zb_head_linear_strided(_ptr(out), _ptr(x), _ptr(w), _ptr(gate), x.stride(0), out.stride(0),
+                                            gate.stride(0) if gate is not None else 0, xhs, yhs, int(per_element),
+                                            x.shape[0], heads, N, K, DTYPE_CODE[x.dtype], DTYPE_CODE[w.dtype],
+                                            DTYPE_CODE[out.dtype], _stream()), "head_linear")
     return out
 
 
@@ -1259,18 +1404,28 @@ def route_max_outputs() -> int:
     return library().zb_route_max_outputs()
 
 
-def route(logits: torch.Tensor, correction: torch.Tensor | None, top: int) -> tuple[torch.Tensor, torch.Tensor]:
-    """Token-choice routing: s = softmax(logits) over all outputs; the ``top`` outputs with the largest
-    s + correction are taken (ties: the lower index), each with the weight s.  Returns (ids int32 [T, top],
-    weights float32 [T, top]), in the order of choice."""
+ROUTE_SCORES = {"softmax": 0, "sigmoid": 1}
+
+
+def route(logits: torch.Tensor, correction: torch.Tensor | None, top: int, scores: str = "softmax",
+          groups: tuple[int, int, int] | None = None, weight_scale: float = 1.0) -> tuple[torch.Tensor, torch.Tensor]:
+    """Token-choice routing: s = softmax(logits) over all outputs (``scores`` "sigmoid": the logistic function
+    of each logit on its own); the ``top`` outputs with the largest s + correction are taken (ties: the lower
+    index), each with the weight s * ``weight_scale``.  ``groups`` = (count, keep, group_top): the outputs
+    form ``count`` equal runs of neighbours, a run's mark is the sum of its ``group_top`` largest choice
+    values, and only outputs of the ``keep`` runs with the largest marks can be taken.  Returns (ids int32
+    [T, top], weights float32 [T, top]), in the order of choice."""
     _cuda(logits, correction)
     _require(logits.dim() == 2 and logits.dtype == torch.float32 and logits.stride(1) == 1, "float32 logits [T, outputs]")
+    _require(scores in ROUTE_SCORES, f"router scores are one of {sorted(ROUTE_SCORES)}")
     T, outputs = logits.shape
     _f32_vector(correction, outputs, "the correction")
+    count, keep, group_top = (int(v) for v in groups) if groups is not None else (1, 1, 1)
     ids = torch.empty((T, top), dtype=torch.int32, device=logits.device)
     weights = torch.empty((T, top), dtype=torch.float32, device=logits.device)
-    _check(library().zb_route(_ptr(ids), _ptr(weights), _ptr(logits), logits.stride(0), _ptr(correction), T, outputs,
-                              int(top), _stream()), "route")
+    _check(library().zb_route_grouped(_ptr(ids), _ptr(weights), _ptr(logits), logits.stride(0), _ptr(correction), T,
+                                      outputs, int(top), ROUTE_SCORES[scores], count, keep, group_top,
+                                      float(weight_scale), _stream()), "route")
     return ids, weights
 
 

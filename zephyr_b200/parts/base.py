@@ -203,13 +203,19 @@ class ResidualStream:
     the stream had it at hand (an input part that writes both); it is void once anything is added."""
 
     hidden: torch.Tensor
-    pending: torch.Tensor | None = None
+    pending: "torch.Tensor | tuple[torch.Tensor, ...] | None" = None    # a tuple: summands that are added to each other first
     deferred: DeferredSum | None = None
     rounded: torch.Tensor | None = None
 
     def flush(self) -> torch.Tensor:
         if self.pending is not None:
-            self.hidden.add_(self.pending)
+            if isinstance(self.pending, tuple):
+                total = self.pending[0].float()
+                for more in self.pending[1:]:
+                    total = total + more.float()
+                self.hidden.add_(total.to(self.hidden.dtype))
+            else:
+                self.hidden.add_(self.pending)
             self.pending = None
         if self.deferred is not None:
             self.deferred.apply(self.hidden)
@@ -238,6 +244,14 @@ class InputPart(Part):
     """Token ids to the first hidden states."""
 
     def __init__(self, spec: InputSpec, weights: Mapping[str, torch.Tensor], dtype: torch.dtype): ...
+
+    # The id of the store ``cache_spec`` asked for, set by the model (the id after the run order's).
+    cache_id: int | None = None
+
+    @staticmethod
+    def cache_spec(spec: InputSpec) -> "StateCacheSpec | None":
+        """What the input part keeps per request between steps (a token it must remember), or None."""
+        return None
 
     def forward(self, ctx: StepContext) -> "torch.Tensor | ResidualStream":
         """[T, hidden] in the model's type for the step's tokens (``ctx.token_ids``), or a whole

@@ -13,6 +13,10 @@ the last one as a ``DeferredSum`` that the next block or the output part takes u
 ``outnorm_residual``: a norm on each part's output only; the parts read the stream itself:
 r = x + mixer_out(mixer(x)); x' = r + ffn_out(ffn(r)).  The stream is float32; in a bfloat16 model the
 parts get its rounding, which the kernel that does a sum writes in the same pass.
+
+``parallel_residual``: one norm, whose output both parts read: h = norm(x); x' = x + (mixer(h) + ffn(h)).
+The stream is float32.  The two summands travel as a pair in ``pending`` and join the stream in the same
+kernel as the next layer's norm (``Norm.sum_forward``).
 """
 
 from __future__ import annotations
@@ -119,6 +123,37 @@ class OutputNormResidual(Block):
         return stream
 
 
+class ParallelResidual(Block):
+    graph_safe = True
+    feed_forward_optional = True
+
+    norm_names = ("input",)
+
+    def __init__(self, mixer: Mixer, feed_forward: FeedForward | None, norms: Mapping[str, Norm], params=None):
+        self.mixer = mixer
+        self.feed_forward = feed_forward
+        self.norms = dict(norms)
+        self.norm = norms["input"]
+        if not hasattr(self.norm, "sum_forward"):
+            raise TypeError("the parallel block needs a norm that adds a pair of summands as it norms (sum_forward)")
+
+    def forward(self, stream: ResidualStream, ctx: StepContext, call: LayerCall) -> ResidualStream:
+        if stream.deferred is not None or stream.hidden.dtype != torch.float32:
+            stream.hidden = stream.flush().float()
+        pending = stream.pending if stream.pending is not None else ()
+        if not isinstance(pending, tuple):
+            pending = (pending,)
+        normed = self.norm.sum_forward(stream.hidden, pending)
+        stream.rounded = None
+        mixed = self.mixer.forward(normed, ctx, call)
+        if self.feed_forward is None:
+            stream.pending = (mixed,)
+        else:
+            stream.pending = (mixed, self.feed_forward.forward(normed))
+        return stream
+
+
 register_block("prenorm_residual", PreNormResidual)
+register_block("parallel_residual", ParallelResidual)
 register_block("outnorm_residual", OutputNormResidual)
 register_block("sandwich_residual", SandwichResidual)

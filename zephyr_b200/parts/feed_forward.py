@@ -1,6 +1,11 @@
 """The dense gated feed-forward: down(act(gate(x)) * up(x)), no biases; act is SiLU (SwiGLU) unless
 the spec's ``activation`` says "relu".
 
+``activation`` "clamped_swish" is the bounded form, with biases on all three products where the spec names
+them: g = min(gate(x), limit), u = clamp(up(x), -limit, limit), y = g * sigmoid(alpha * g) * (u + up_shift),
+out = down(y).  Biases, bounds and the activation are one float32 pass over the unrounded product; the
+down product's bias joins its float32 sums, and the part then hands out float32.
+
 Gate and up run as one product over one packed weight [2I, H], as the reference packs them at
 load (src/layer/mlp.cpp:16-36); the reference puts all gate rows first, this part alternates blocks
 of 8 gate rows and 8 up rows (see ``__init__``).  silu and the product are one float32
@@ -16,7 +21,7 @@ import torch
 from ..config.errors import ConfigError
 from ..config.spec import FeedForwardSpec
 from ..kernels import ops
-from ..weights.loader import ROLE_LINEAR, WeightDecl
+from ..weights.loader import ROLE_LINEAR, ROLE_ZERO, WeightDecl
 from .base import FeedForward, register_feed_forward
 
 
@@ -28,8 +33,20 @@ class SwiGLU(FeedForward):
         self.hidden = int(p["hidden_size"])
         self.intermediate = int(p["intermediate_size"])
         self.activation = str(p.get("activation", "silu"))
-        if self.activation not in ops.ACTIVATIONS:
-            raise ConfigError(f"a gated feed-forward's activation is one of {sorted(ops.ACTIVATIONS)}")
+        self.clamped = self.activation == "clamped_swish"
+        if self.activation not in ops.ACTIVATIONS and not self.clamped:
+            raise ConfigError(f"a gated feed-forward's activation is one of {sorted(ops.ACTIVATIONS) + ['clamped_swish']}")
+        self.dtype = dtype
+        self.limit = float(p.get("limit", 0.0))
+        self.alpha = float(p.get("alpha", 1.0))
+        self.up_shift = float(p.get("up_shift", 0.0))
+        if self.clamped and not self.limit > 0.0:
+            raise ConfigError("the bounded activation needs a positive limit")
+        has_bias = [bool(p.get(k)) for k in ("gate_bias", "up_bias", "down_bias")]
+        if any(has_bias) and not self.clamped:
+            raise ConfigError("biases come with the bounded activation only")
+        if has_bias[0] != has_bias[1]:
+            raise ConfigError("gate and up carry biases together or not at all")
         gate, up = weights[p["gate_proj"]], weights[p["up_proj"]]
         # With I a multiple of 8 the rows alternate in blocks of 8 gate rows and their 8 up rows, the
         # order in which the decode kernel applies silu(gate) * up inside the product's epilogue.
@@ -40,22 +57,42 @@ class SwiGLU(FeedForward):
         else:
             self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
         self.w_down = weights[p["down_proj"]]
+        self.b_gate_up = self.b_down = None
+        if has_bias[0]:
+            b_gate, b_up = weights[p["gate_bias"]].float(), weights[p["up_bias"]].float()
+            if self.blocked:
+                self.b_gate_up = torch.stack([b_gate.view(-1, 8), b_up.view(-1, 8)], dim=1).reshape(-1).contiguous()
+            else:
+                self.b_gate_up = torch.cat([b_gate, b_up]).contiguous()
+        if has_bias[2]:
+            self.b_down = weights[p["down_bias"]].float().contiguous()
 
     @staticmethod
     def weight_decls(spec: FeedForwardSpec) -> dict[str, WeightDecl]:
         p = spec.params
         hidden, inter = int(p["hidden_size"]), int(p["intermediate_size"])
-        return {
+        decls = {
             p["gate_proj"]: WeightDecl((inter, hidden), ROLE_LINEAR),
             p["up_proj"]: WeightDecl((inter, hidden), ROLE_LINEAR),
             p["down_proj"]: WeightDecl((hidden, inter), ROLE_LINEAR),
         }
+        for key, size in (("gate_bias", inter), ("up_bias", inter), ("down_bias", hidden)):
+            if p.get(key):
+                decls[p[key]] = WeightDecl((size,), ROLE_ZERO)
+        return decls
 
     def as_gated_products(self) -> tuple[torch.Tensor, torch.Tensor] | None:
         # The chain of small products has SiLU in its epilogue; another activation keeps the layer off it.
         return (self.w_gate_up, self.w_down) if self.blocked and self.activation == "silu" else None
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self.clamped:
+            product = ops.linear(x, self.w_gate_up, out_dtype=torch.float32)
+            hidden = ops.clamped_gate(product, self.b_gate_up, self.limit, self.alpha, self.up_shift, self.dtype,
+                                      blocked=self.blocked)
+            if self.b_down is None:
+                return ops.linear(hidden, self.w_down)
+            return ops.add_bias(ops.linear(hidden, self.w_down, out_dtype=torch.float32), self.b_down)
         act = self.activation
         if self.blocked and x.shape[0] <= ops.SMALL_GEMM_ROWS and ops.gemm_small_supported(x, self.w_gate_up):
             hidden = ops.gemm_small(x, self.w_gate_up, swiglu=True, act=act)       # product and activation in one kernel

@@ -8,7 +8,15 @@ position, and only the latent is cached.
                                                spec names sinks (a term without key or value)
     o_i = sum_j p_ij v_j,  times sigmoid(Wg h)_h where the spec names a gate;  out = Wo concat(o)
 
-There is no position encoding.  The part works in the latent space, which is what makes caching c alone
+Optional pieces, each named by the spec: queries through a latent of their own (c_q = rmsnorm(Wdq h) w_q,
+q = Wuq c_q); a rotated part (``rot_dim`` > 0 with a position encoding that offers ``as_half_frequencies``:
+every query head carries ``rot_dim`` more values behind its ``dim`` unrotated ones, the latent projection
+``rot_dim`` more rows that form ONE rotated key part shared by all heads, and the score is
+q_unrotated . k_unrotated + q_rotated . k_rotated; the cached row is then the normed latent followed by
+the rotated key part, and the values are maps of its first ``rank`` entries); a gate per output value
+instead of one per head (a gate matrix of heads * vdim rows).
+
+Without a rotated part there is no position encoding.  The part works in the latent space, which is what makes caching c alone
 enough: q_i . (Wuk_h c_j) = (Wuk_h^T q_i) . c_j and sum_j p_ij Wuv_h c_j = Wuv_h (sum_j p_ij c_j).  So the
 queries are carried into the latent space head by head (``ops.head_linear`` with the transposed key
 maps), the attention runs with ONE key/value head of width ``rank`` whose keys are its values (a cache
@@ -27,7 +35,7 @@ from ..config.errors import ConfigError
 from ..config.spec import LayerCall, MixerSpec
 from ..kernels import ops
 from ..weights.loader import ROLE_LINEAR, ROLE_NORM, ROLE_ZERO, WeightDecl
-from .base import Mixer, StepContext, register_mixer
+from .base import POSITION_ENCODINGS, Mixer, StepContext, lookup, register_mixer
 
 
 class LatentAttention(Mixer):
@@ -44,51 +52,75 @@ class LatentAttention(Mixer):
         self.dtype = dtype
         if min(self.nh, self.hd, self.vd, self.rank) <= 0:
             raise ConfigError("latent attention needs positive head count, head sizes and rank")
-        if self.rank > 512:
-            raise ConfigError(f"latent attention takes a latent size of at most 512, not {self.rank}")
+        self.rot = int(p.get("rot_dim", 0))
+        self.kw = self.rank + self.rot            # what a position keeps: the latent and the rotated key part
+        if self.kw > 512:
+            raise ConfigError(f"latent attention keeps at most 512 values a position, not {self.kw}")
+        self.position = None
+        self.freqs, self.rope_mult = None, 1.0
+        if self.rot > 0:
+            if spec.position is None:
+                raise ConfigError("a rotated part needs a position encoding")
+            self.position = lookup(POSITION_ENCODINGS, "position encoding", spec.position.kind)(spec.position, dtype, device)
+            halves = getattr(self.position, "as_half_frequencies", None)
+            if halves is None or halves()[1] != self.rot:
+                raise ConfigError("latent attention rotates the halves of its whole rotated part (dims = rot_dim)")
+            self.freqs, _, self.rope_mult = halves()
         nh, hd, vd, rank = self.nh, self.hd, self.vd, self.rank
         gate = weights[p["gate"]] if p.get("gate") else None
-        # One product for everything that reads the layer's input: queries, the latent, the gates.
-        rows = [weights[p["q_proj"]], weights[p["latent_proj"]]] + ([gate] if gate is not None else [])
+        # One product for everything that reads the layer's input: queries (or their latent), the latent, the gates.
+        self.q_rank = int(p["q_rank"]) if p.get("q_down") else 0
+        first = weights[p["q_down"]] if self.q_rank else weights[p["q_proj"]]
+        rows = [first, weights[p["latent_proj"]]] + ([gate] if gate is not None else [])
         self.w_in = torch.cat(rows, dim=0).contiguous()
+        self.q_cols = first.shape[0]
+        self.w_q_up = weights[p["q_proj"]] if self.q_rank else None
+        self.q_norm = weights[p["q_down_norm"]].float().contiguous() if self.q_rank else None
         self.has_gate = gate is not None
         self.latent_norm = weights[p["latent_norm"]].float().contiguous()
         # Per head [rank, dim]: the key map transposed, so that it carries a query into the latent space.
         self.w_q_to_latent = weights[p["k_up"]].view(nh, hd, rank).transpose(1, 2).contiguous()
+        if gate is not None and gate.shape[0] not in (nh, nh * vd):
+            raise ConfigError("a gate has one row per head or one per output value")
         self.w_latent_to_v = weights[p["v_up"]].view(nh, vd, rank).contiguous()
         self.w_o = weights[p["o_proj"]]
         self.sinks = weights[p["sinks"]].float().contiguous() if p.get("sinks") else None
         self.tile_tokens = ops.attention_tile_tokens(nh)
         # In bfloat16 the split-context decode kernel and the tensor-core prompt kernel take the latent
         # as one key/value head whose keys are its values, where they take its width and head count.
-        self.fast_decode = ops.paged_decode_supported(nh, 1, rank, dtype)
-        self.fast_prefill = ops.paged_prefill_supported(nh, 1, rank, dtype)
+        self.fast_decode = ops.paged_decode_supported(nh, 1, self.kw, dtype)
+        self.fast_prefill = ops.paged_prefill_supported(nh, 1, self.kw, dtype)
         self.prefill_tile_tokens = ops.paged_prefill_tile_tokens()
 
     @staticmethod
     def weight_decls(spec: MixerSpec) -> dict[str, WeightDecl]:
         p = spec.params
         hidden, nh, hd, vd, rank = (int(p[k]) for k in ("hidden_size", "num_heads", "head_dim", "value_dim", "rank"))
+        rot = int(p.get("rot_dim", 0))
         decls = {
-            p["q_proj"]: WeightDecl((nh * hd, hidden), ROLE_LINEAR),
-            p["latent_proj"]: WeightDecl((rank, hidden), ROLE_LINEAR),
+            p["q_proj"]: WeightDecl((nh * (hd + rot), int(p["q_rank"]) if p.get("q_down") else hidden), ROLE_LINEAR),
+            p["latent_proj"]: WeightDecl((rank + rot, hidden), ROLE_LINEAR),
             p["latent_norm"]: WeightDecl((rank,), ROLE_NORM),
             p["k_up"]: WeightDecl((nh * hd, rank), ROLE_LINEAR),
             p["v_up"]: WeightDecl((nh * vd, rank), ROLE_LINEAR),
             p["o_proj"]: WeightDecl((hidden, nh * vd), ROLE_LINEAR),
         }
+        if p.get("q_down"):
+            decls[p["q_down"]] = WeightDecl((int(p["q_rank"]), hidden), ROLE_LINEAR)
+            decls[p["q_down_norm"]] = WeightDecl((int(p["q_rank"]),), ROLE_NORM)
         if p.get("gate"):
-            decls[p["gate"]] = WeightDecl((nh, hidden), ROLE_LINEAR)
+            decls[p["gate"]] = WeightDecl((nh * vd if p.get("gate_per_element") else nh, hidden), ROLE_LINEAR)
         if p.get("sinks"):
             decls[p["sinks"]] = WeightDecl((nh,), ROLE_ZERO)
         return decls
 
     def weights_read(self) -> list[torch.Tensor]:
-        return [self.w_in, self.w_q_to_latent, self.w_latent_to_v, self.w_o, self.latent_norm]
+        return [w for w in (self.w_in, self.w_q_up, self.q_norm, self.w_q_to_latent, self.w_latent_to_v, self.w_o,
+                            self.latent_norm) if w is not None]
 
     @staticmethod
     def cache_spec(spec: MixerSpec) -> PagedCacheSpec:
-        return PagedCacheSpec(1, key_dim=int(spec.params["rank"]), keys_only=True)
+        return PagedCacheSpec(1, key_dim=int(spec.params["rank"]) + int(spec.params.get("rot_dim", 0)), keys_only=True)
 
     @staticmethod
     def tile_requests(spec: MixerSpec) -> list[tuple[int, str]]:
@@ -97,26 +129,42 @@ class LatentAttention(Mixer):
 
     def forward(self, x: torch.Tensor, ctx: StepContext, call: LayerCall,
                 out_dtype: torch.dtype | None = None) -> torch.Tensor:
-        nh, hd, rank = self.nh, self.hd, self.rank
+        nh, hd, rank, rot, kw = self.nh, self.hd, self.rank, self.rot, self.kw
         table = ctx.block_table(call.cache)
         cache = ctx.caches[call.cache]
-        projected = ops.linear(x, self.w_in, out_dtype=torch.float32)          # [T, nh*hd + rank (+ nh)]
-        if call.writes_cache:
-            # The latent's norm and its place in the pages, one kernel; nothing else is kept of a position.
-            ops.qkv_pairs(projected[:, nh * hd: nh * hd + rank], 0, 1, rank, 0, None, None, self.latent_norm, self.eps,
-                          None, 0, ctx.positions, ctx.token_row, cache, table, ctx.status, self.dtype)
-        q_latent = ops.head_linear(projected[:, : nh * hd], self.w_q_to_latent)  # [T, nh * rank], the model's type
+        projected = ops.linear(x, self.w_in, out_dtype=torch.float32)          # [T, queries | latent (+ rotated key) | gates]
+        at = self.q_cols
+        if self.q_rank:
+            # The queries' own latent: its norm in float32, then the map to the heads (kept unrounded).
+            q_latent_in = ops.sum_rms_norm(projected[:, :at], None, None, self.q_norm, self.eps, out_dtype=self.dtype)
+            queries = ops.linear(q_latent_in, self.w_q_up, out_dtype=torch.float32)
+        else:
+            queries = projected[:, :at]
+        if rot == 0:
+            if call.writes_cache:
+                # The latent's norm and its place in the pages, one kernel; nothing else is kept of a position.
+                ops.qkv_pairs(projected[:, at: at + rank], 0, 1, rank, 0, None, None, self.latent_norm, self.eps,
+                              None, 0, ctx.positions, ctx.token_row, cache, table, ctx.status, self.dtype)
+            q_latent = ops.head_linear(queries, self.w_q_to_latent)             # [T, nh * rank], the model's type
+        else:
+            # Every head's unrotated part is carried into the latent space; its rotated part follows it as it
+            # is (turned by the position), so that one dot product with the cached row gives both terms.
+            q_latent = torch.empty((x.shape[0], nh * kw), dtype=self.dtype, device=x.device)
+            ops.head_linear(queries, self.w_q_to_latent, x_head_stride=hd + rot, out=q_latent, out_head_stride=kw)
+            ops.latent_rope(queries, nh, hd + rot, hd, q_latent, projected[:, at: at + kw], rank, rot, self.latent_norm,
+                            self.eps, self.freqs, self.rope_mult, ctx.positions, ctx.token_row,
+                            cache if call.writes_cache else None, table, ctx.status, self.dtype)
         attended = self.attend(q_latent, ctx, cache, table)
-        gate = projected[:, nh * hd + rank:] if self.has_gate else None
-        heads_out = ops.head_linear(attended, self.w_latent_to_v, gate=gate)     # [T, nh * vd]
+        gate = projected[:, at + kw:] if self.has_gate else None
+        heads_out = ops.head_linear(attended, self.w_latent_to_v, gate=gate, x_head_stride=kw)     # [T, nh * vd]
         return ops.linear(heads_out, self.w_o, out_dtype=out_dtype)
 
     def attend(self, q: torch.Tensor, ctx: StepContext, cache: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
-        """Attention of the latent-space queries [T, heads * rank] over the cached latents: rows with one
+        """Attention of the latent-space queries [T, heads * (rank + rot)] over the cached rows: rows with one
         new token on the split-context kernel, rows with several on the tensor-core prompt kernel, where
         those take this shape and type; whatever is left on the general kernel."""
         out = torch.empty_like(q)
-        common = (self.nh, 1, self.rank, 0, self.scale, ctx.status)
+        common = (self.nh, 1, self.kw, 0, self.scale, ctx.status)
         decode_done = self.fast_decode and ctx.num_decode_rows > 0
         if decode_done:
             ops.paged_decode(q, cache, table, ctx.decode_rows, ctx.row_q_start, ctx.row_ctx, ctx.max_decode_context,

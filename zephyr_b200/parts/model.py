@@ -75,6 +75,10 @@ def cache_specs(spec: ModelSpec) -> list[PagedCacheSpec | StateCacheSpec | None]
                 out[cache] = need
             elif out[cache] != need:
                 raise ConfigError(f"layer {call.layer} reads cache {cache}, whose shape does not fit its mixer")
+    # An input part that remembers something per request gets the id after the run order's.
+    need = lookup(INPUTS, "input part", spec.input.kind).cache_spec(spec.input)
+    if need is not None:
+        out.append(need)
     return out
 
 
@@ -117,6 +121,8 @@ class Model:
                                      {name: cls(layer.norms[name], weights, dtype) for name, cls in norms.items()},
                                      **extra))
         self.cache_specs = cache_specs(spec)
+        if len(self.cache_specs) > spec.num_caches:
+            self.input.cache_id = spec.num_caches
         parts = [self.input, self.output]
         for block in self.layers:
             parts += [block, block.mixer, block.feed_forward, *getattr(block, "norms", {}).values(),
@@ -212,8 +218,8 @@ class Model:
     def forward(self, ctx: StepContext) -> torch.Tensor:
         """Run the step's tokens through the model; float32 logits [wanted, vocab]."""
         hidden = self.input.forward(ctx)
-        if isinstance(hidden, ResidualStream):
-            stream = hidden
+        if isinstance(hidden, ResidualStream) or hidden.dtype != self.dtype:      # a float32 stream: layer by layer
+            stream = hidden if isinstance(hidden, ResidualStream) else ResidualStream(hidden)
             for call in self.spec.run_order:
                 stream = self.layers[call.layer].forward(stream, ctx, call)
             return self.output.forward(stream, ctx)

@@ -22,6 +22,7 @@ class RMSNorm(Norm):
     def __init__(self, spec: NormSpec, weights: Mapping[str, torch.Tensor], dtype: torch.dtype):
         self.size = spec.size
         self.eps = float(spec.eps)
+        self.dtype = dtype
         self.weight = weights[spec.weight]
 
     @staticmethod
@@ -29,7 +30,18 @@ class RMSNorm(Norm):
         return {spec.weight: WeightDecl((spec.size,), ROLE_NORM)}
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if x.dtype == torch.float32 and self.dtype != torch.float32:
+            return ops.sum_rms_norm(x, None, None, self.weight, self.eps, out_dtype=self.dtype)    # a float32 stream
         return ops.rmsnorm(x, self.weight, self.eps)
+
+    def sum_forward(self, stream: torch.Tensor, summands: tuple) -> torch.Tensor:
+        """stream (float32) += (the first summand + the second), in place and in float32; returns the norm
+        of the sum in the model's type.  One kernel for the sums and the norm."""
+        a = summands[0] if len(summands) > 0 else None
+        b = summands[1] if len(summands) > 1 else None
+        for more in summands[2:]:
+            stream.add_(more)
+        return ops.sum_rms_norm(stream, a, b, self.weight, self.eps, out_dtype=self.dtype)
 
     def add_forward(self, residual: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
         return ops.add_rmsnorm(residual, delta, self.weight, self.eps)

@@ -8,6 +8,10 @@ tables stay float32 on the device (the reference rounds them to the model's type
 ``rope_pairs``: rotation of adjacent pairs (2i, 2i + 1) on the first ``dims`` dimensions of a head, with
 optional scaling of the frequencies by wavelength.
 
+``rope_halves``: rotation of the pairs (i, i + dims/2) on the first ``dims`` dimensions of a head, angles
+formed on the device as float32 products, with optional YaRN scaling of the frequencies and its
+multiplier on cosine and sine.
+
 ``none``: no encoding.
 """
 
@@ -129,6 +133,66 @@ class RopePairs(PositionEncoding):
         raise ConfigError("the rotation of adjacent pairs runs inside the attention's own kernel only")
 
 
+def yarn_frequencies(freqs: list[float], dims: int, base: float, factor: float, original: float, fast: float,
+                     slow: float) -> tuple[list[float], float]:
+    """YaRN: frequencies that turn often within the ``original`` context stay, those that turn seldom are
+    divided by ``factor``, with a linear ramp over the dimension index in between.  The dimension whose
+    frequency makes t turns over ``original`` positions is d(t) = dims ln(original / (2 pi t)) / (2 ln base);
+    the ramp runs from lo = max(floor(d(fast)), 0) to hi = min(ceil(d(slow)), dims - 1):
+    r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), f_i' = r_i f_i / factor + (1 - r_i) f_i.
+    Returns the frequencies and the multiplier 0.1 ln(factor) + 1 that goes on cosine and sine."""
+    def turns_to_dim(turns: float) -> float:
+        return dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
+
+    lo = max(math.floor(turns_to_dim(fast)), 0)
+    hi = min(math.ceil(turns_to_dim(slow)), dims - 1)
+    out = []
+    for i, f in enumerate(freqs):
+        ramp = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+        out.append(f / factor * ramp + f * (1.0 - ramp))
+    return out, 0.1 * math.log(factor) + 1.0
+
+
+class RopeHalves(PositionEncoding):
+    """Rotation of halves: dimension i of the rotated part pairs with dimension i + dims / 2, i < dims / 2;
+    (u, v) -> (u c - v s, v c + u s) with c = m cos(p f_i), s = m sin(p f_i), f_i = base^(-2i / dims).
+    ``params``: base, dims (default: the head size), scaling (None, or factor / original / fast / slow as in
+    ``yarn_frequencies``, which also sets m; m = 1 without).  Frequencies are worked out in double
+    precision on the host and kept as float32; angles are float32 products on the device.  Mixers hand
+    frequencies and multiplier to their own kernels (``as_half_frequencies``); ``apply`` is not offered."""
+
+    graph_safe = True
+
+    kind = "rope_halves"
+
+    def __init__(self, spec: PositionSpec, dtype: torch.dtype, device: torch.device | str):
+        dims = int(spec.params.get("dims", spec.head_dim))
+        base = float(spec.params.get("base", 10000.0))
+        if dims <= 0 or dims % 2 != 0 or dims > spec.head_dim:
+            raise ConfigError("rotated dimensions must be even, positive and no more than the head size")
+        if not base > 1.0 or base == float("inf"):
+            raise ConfigError("the rotary base must be finite and greater than one")
+        freqs = [base ** (-2.0 * i / dims) for i in range(dims // 2)]
+        self.mult = 1.0
+        scaling = spec.params.get("scaling")
+        if scaling:
+            factor, original, fast, slow = (float(scaling[k]) for k in ("factor", "original", "fast", "slow"))
+            if factor <= 0.0 or original <= 0.0 or fast <= 0.0 or slow <= 0.0:
+                raise ConfigError("YaRN scaling needs positive factor, original, fast and slow")
+            freqs, self.mult = yarn_frequencies(freqs, dims, base, factor, original, fast, slow)
+        self.head_dim = spec.head_dim
+        self.dims = dims
+        self.max_positions = spec.max_positions
+        self.freqs = torch.tensor(freqs, dtype=torch.float64).to(torch.float32).to(device)
+
+    def as_half_frequencies(self) -> tuple[torch.Tensor, int, float]:
+        return self.freqs, self.dims, self.mult
+
+    def apply(self, x: torch.Tensor, heads: int, positions: torch.Tensor, status: torch.Tensor) -> torch.Tensor:
+        raise ConfigError("the rotation of halves with scaled frequencies runs inside a mixer's own kernel only")
+
+
 register_position_encoding("rope_neox", RopeNeox)
+register_position_encoding("rope_halves", RopeHalves)
 register_position_encoding("rope_pairs", RopePairs)
 register_position_encoding("none", NoPosition)

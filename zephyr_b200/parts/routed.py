@@ -6,6 +6,11 @@
     the ``top`` outputs with the largest choice are taken; each counts with its s (not renormalised)
     out = sum over the taken outputs e of  s_e * expert_e(x)
 
+Further forms, each named by the spec: ``scores`` "sigmoid" (s = sigmoid(z), every output on its own);
+``groups`` = {count, keep, top}: the outputs form ``count`` equal runs of neighbours, a run's mark is the sum of
+its ``top`` largest choice values, and only outputs of the ``keep`` runs with the largest marks can be taken;
+``weight_scale``: a multiplier on every weight.
+
 The first ``experts`` router outputs are gated feed-forwards, expert_e(x) = down_e(act(gate_e x) * (up_e x)),
 without biases; the last ``identity`` outputs are identity experts, expert(x) = x, which have no tensors.
 Every expert's matrices are stacked at load ([experts, ff, hidden] and [experts, hidden, ff]) so that
@@ -41,6 +46,19 @@ class RoutedFeedForward(FeedForward):
             raise ConfigError("a routed feed-forward needs experts, and takes between one and all of its outputs")
         if self.activation not in ops.ACTIVATIONS:
             raise ConfigError(f"an expert's activation is one of {sorted(ops.ACTIVATIONS)}")
+        self.scores = str(p.get("scores", "softmax"))
+        if self.scores not in ops.ROUTE_SCORES:
+            raise ConfigError(f"router scores are one of {sorted(ops.ROUTE_SCORES)}")
+        self.weight_scale = float(p.get("weight_scale", 1.0))
+        self.groups = None
+        if p.get("groups"):
+            g = p["groups"]
+            count, keep, group_top = int(g["count"]), int(g["keep"]), int(g.get("top", 2))
+            if (count <= 0 or outputs % count != 0 or not 0 < keep <= count or group_top <= 0
+                    or keep * (outputs // count) < self.top):
+                raise ConfigError("router groups must divide the outputs evenly, and the kept groups must hold the choices")
+            if count > 1:
+                self.groups = (count, keep, group_top)
         self.w_router = weights[p["router"]]
         self.correction = weights[p["correction"]].float().contiguous() if p.get("correction") else None
         if outputs > ops.route_max_outputs():
@@ -75,7 +93,7 @@ class RoutedFeedForward(FeedForward):
 
     def route(self, x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
         logits = ops.linear(x, self.w_router, out_dtype=torch.float32)
-        return ops.route(logits, self.correction, self.top)
+        return ops.route(logits, self.correction, self.top, self.scores, self.groups, self.weight_scale)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         ids, weights = self.route(x)
