@@ -57,6 +57,18 @@ GEFOVIK_SIZES = {
                   identity=2, top=4),
 }
 
+# ``--arch fekotar``: the same for the design whose layers run latent attention (queries through a latent of
+# their own, a rotated part, a gate per value) and a feed-forward side by side on one norm's output;
+# feed-forwards bounded dense and routed (16 experts in 4 groups of which 2 are kept, a token takes 4) in
+# turn.  A position keeps kv_rank + rot_dim = 128 values.  Beside it runs Gefovik, the closest design the
+# engine has, with latent attention over a latent of 128 in every layer and the same feed-forward sizes.
+FEKOTAR_SIZES = {
+    "w2048": dict(width=2048, ff=6144, layers=8, heads=16, dim=128, rot_dim=32, vdim=128, kv_rank=96, q_rank=768, experts=16, top=4,
+                  groups=(4, 2)),
+    "w4096": dict(width=4096, ff=12288, layers=8, heads=16, dim=128, rot_dim=32, vdim=128, kv_rank=96, q_rank=1536, experts=16, top=4,
+                  groups=(4, 2)),
+}
+
 
 def metric_name(args) -> str:
     """One string for both arms: the driver divides their values only if the strings are equal."""
@@ -237,6 +249,32 @@ def build_gefovik_pair(size: str, batch: int, context: int):
     return gefovik, qwen, make
 
 
+def build_fekotar_pair(size: str, batch: int, context: int):
+    """(Fekotar configuration, Gefovik configuration of equal sizes, engine builder) of one entry of ``FEKOTAR_SIZES``."""
+    from zephyr_b200.config import FekotarConfig, GefovikConfig
+
+    z = FEKOTAR_SIZES[size]
+    scale = (z["dim"] + z["rot_dim"]) ** -0.5
+    mixer = dict(heads=z["heads"], dim=z["dim"], rot_dim=z["rot_dim"], vdim=z["vdim"], kv_rank=z["kv_rank"], q_rank=z["q_rank"],
+                 scale=scale, rot={"base": 10000.0, "dims": z["rot_dim"],
+                                   "scaling": {"factor": 40.0, "original": 4096, "fast": 32.0, "slow": 1.0}})
+    router = {"experts": z["experts"], "top": z["top"], "scale": 2.5, "groups": {"count": z["groups"][0], "keep": z["groups"][1]}}
+    dense = {"kind": "dense", "ff": z["ff"], "limit": 7.0}
+    routed = {"kind": "moe", "expert": {"ff": z["ff"] // z["top"]}, "router": router}
+    fekotar = FekotarConfig(vocab=32768, width=z["width"], norm_eps=1e-6, logit_scale=0.25,
+                            bigram={"buckets": 65521, "mul_prev": 36313, "mul_cur": 27191},
+                            layers=tuple({"type": "latent_attention", "mixer": mixer, "mlp": mlp}
+                                         for mlp in [dense, routed] * (z["layers"] // 2)))
+    latent = dict(heads=z["heads"], dim=z["dim"], vdim=z["vdim"], kv_rank=z["kv_rank"] + z["rot_dim"], scale=z["dim"] ** -0.5)
+    old_dense = {"kind": "dense", "ff": z["ff"]}
+    old_routed = {"kind": "moe", "expert": {"ff": z["ff"] // z["top"]}, "router": {"experts": z["experts"], "identity": 0, "top": z["top"]}}
+    gefovik = GefovikConfig(vocab=32768, width=z["width"], norm_eps=1e-6, embedding_scale=1.0,
+                            layers=tuple({"type": "latent_attention", "mixer": latent, "mlp": mlp}
+                                         for mlp in [old_dense, old_routed] * (z["layers"] // 2)))
+    _, _, make = build_pair("w2048", batch, context)
+    return fekotar, gefovik, make
+
+
 def run_legelix(args) -> dict:
     """Prefill of 2048 tokens and a decode step of ``--batch`` requests at ``--context``, device-timed, for
     every entry of ``LEGELIX_SIZES`` (or ``GEFOVIK_SIZES``) and for the Qwen3 decoder of equal size beside it."""
@@ -246,11 +284,12 @@ def run_legelix(args) -> dict:
 
     out = {"arch": args.arch, "batch": args.batch, "context": args.context, "prefill_tokens": PREFILL_TOKENS, "dtype": "bf16",
            "data": "synthetic: seeded random weights and token ids", "sizes": {}}
-    table, pair = (LEGELIX_SIZES, build_pair) if args.arch == "legelix" else (GEFOVIK_SIZES, build_gefovik_pair)
+    table, pair, beside = {"legelix": (LEGELIX_SIZES, build_pair, "qwen3"), "gefovik": (GEFOVIK_SIZES, build_gefovik_pair, "qwen3"),
+                           "fekotar": (FEKOTAR_SIZES, build_fekotar_pair, "gefovik")}[args.arch]
     for size in (args.sizes.split(",") if args.sizes else table):
         legelix, qwen, make = pair(size, args.batch, args.context)
         row = {}
-        for name, config in ((args.arch, legelix), ("qwen3", qwen)):
+        for name, config in ((args.arch, legelix), (beside, qwen)):
             engine = make(config)
             prefill_ms = device_prefill(engine, PREFILL_TOKENS, 3, 5)
             decode_ms, launches, _ = device_decode(engine, args.batch, args.context, args.warmup, args.steps, None)
@@ -548,9 +587,10 @@ def main() -> int:
     parser.add_argument("--no-points", dest="points", action="store_false", help="skip decode at batch 1 and 64")
     parser.add_argument("--own-products", action="store_true",
                         help="with --only: no product on the vendor library (all on this package's tcgen05 kernel)")
-    parser.add_argument("--arch", choices=("qwen3", "legelix", "gefovik"), default="qwen3",
-                        help="legelix, gefovik: prefill and decode of that design at a few layer sizes, beside Qwen3 of equal size")
-    parser.add_argument("--sizes", default="", help="--arch legelix|gefovik: entries of LEGELIX_SIZES or GEFOVIK_SIZES, with commas (default: all)")
+    parser.add_argument("--arch", choices=("qwen3", "legelix", "gefovik", "fekotar"), default="qwen3",
+                        help="legelix, gefovik: prefill and decode of that design at a few layer sizes, beside Qwen3 of equal "
+                             "size; fekotar: the same beside Gefovik of equal size")
+    parser.add_argument("--sizes", default="", help="--arch legelix|gefovik|fekotar: entries of that design's table of sizes, with commas (default: all)")
     parser.add_argument("--only", choices=("prefill", "decode"), default=None,
                         help="time only the 2048-token prefill, or only the decode step, and print a short line "
                              "(the program a profiler is pointed at)")
@@ -560,7 +600,7 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
-    if args.arch in ("legelix", "gefovik"):
+    if args.arch in ("legelix", "gefovik", "fekotar"):
         print(json.dumps(run_legelix(args)))
         return 0
     if args.only is not None and args.impl == "ours":

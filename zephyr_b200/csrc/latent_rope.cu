@@ -10,12 +10,14 @@
 // Rotation of halves: value i pairs with value i + rot/2,
 //   (u, v) -> (u c - v s, v c + u s),  c = m cos(p f_i), s = m sin(p f_i),
 // the angle p f_i a float32 product, f a table of float32 frequencies made by the host, m one
-// multiplier on both cosine and sine.  One warp per (token, head), warp 0 of a token for the cached row.
+// multiplier on both cosine and sine.  One CTA per token: the position's cosines and sines once, then a
+// (head, pair) a thread for the queries, and the first warp for the cached row.
 #include "common.cuh"
 
 namespace zb {
 
-constexpr int LR_WARPS = 4;
+constexpr int LR_THREADS = 128;
+constexpr int LR_MAX_HALF = 256;     // rotated parts of up to 512 values
 
 struct LatentRopeArgs {
   const float* kv;          // [T, kv_stride]: rank latent values, then rot key values
@@ -38,26 +40,31 @@ struct LatentRopeArgs {
 };
 
 template <typename T>
-__global__ void __launch_bounds__(LR_WARPS * 32) latent_rope_kernel(const LatentRopeArgs a) {
-  const int t = blockIdx.x, lane = threadIdx.x & 31;
-  const int unit = blockIdx.y * LR_WARPS + (threadIdx.x >> 5);      // 0: the cached row; 1 + h: query head h
-  if (unit > a.nh) return;
+__global__ void __launch_bounds__(LR_THREADS) latent_rope_kernel(const LatentRopeArgs a) {
+  __shared__ float cos_of[LR_MAX_HALF], sin_of[LR_MAX_HALF];
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int pos = a.positions[t], half = a.rot / 2, width = a.rank + a.rot;
-  if (unit > 0) {
-    const int h = unit - 1;
-    const float* src = a.q + static_cast<long long>(t) * a.q_stride + static_cast<long long>(h) * a.q_head_stride + a.q_rot_offset;
-    T* dst = static_cast<T*>(a.q_out) + (static_cast<long long>(t) * a.nh + h) * width + a.rank;
-    for (int i = lane; i < half; i += 32) {
-      float s, c;
-      sincosf(static_cast<float>(pos) * a.freqs[i], &s, &c);
-      s *= a.mult; c *= a.mult;
-      const float u = src[i], v = src[i + half];
-      dst[i] = from_float<T>(u * c - v * s);
-      dst[i + half] = from_float<T>(v * c + u * s);
-    }
-    return;
+  // The position's angles once for all heads.
+  for (int i = threadIdx.x; i < half; i += LR_THREADS) {
+    float s, c;
+    sincosf(static_cast<float>(pos) * a.freqs[i], &s, &c);
+    cos_of[i] = c * a.mult;
+    sin_of[i] = s * a.mult;
   }
-  if (a.cache == nullptr) return;
+  __syncthreads();
+  // The queries' rotated parts: one (head, pair) a thread and step.
+  const float* q_row = a.q + static_cast<long long>(t) * a.q_stride + a.q_rot_offset;
+  T* q_dst = static_cast<T*>(a.q_out) + static_cast<long long>(t) * a.nh * width + a.rank;
+  for (int item = threadIdx.x; item < a.nh * half; item += LR_THREADS) {
+    const int h = item / half, i = item - h * half;
+    const float* src = q_row + static_cast<long long>(h) * a.q_head_stride;
+    const float u = src[i], v = src[i + half], c = cos_of[i], s = sin_of[i];
+    T* dst = q_dst + static_cast<long long>(h) * width;
+    dst[i] = from_float<T>(u * c - v * s);
+    dst[i + half] = from_float<T>(v * c + u * s);
+  }
+  if (a.cache == nullptr || warp != 0) return;
+  // The cached row, by the first warp: the normed latent, then the rotated key part.
   const int row = a.token_row[t], block = pos / a.page_size;
   if (row < 0 || row >= a.num_rows || block >= a.max_blocks || pos < 0) {
     if (lane == 0) report(a.status, STATUS_ROW_OUT_OF_RANGE, row, t);
@@ -79,10 +86,7 @@ __global__ void __launch_bounds__(LR_WARPS * 32) latent_rope_kernel(const Latent
     dst[at] = from_float<T>(src[i] * inv * a.norm_w[i]);
   }
   for (int i = lane; i < half; i += 32) {
-    float s, c;
-    sincosf(static_cast<float>(pos) * a.freqs[i], &s, &c);
-    s *= a.mult; c *= a.mult;
-    const float u = src[a.rank + i], v = src[a.rank + i + half];
+    const float u = src[a.rank + i], v = src[a.rank + i + half], c = cos_of[i], s = sin_of[i];
     const int lo = a.rank + i, hi = a.rank + i + half;
     dst[swizzled ? kv_element_index(lo, pos, width, sizeof(T)) : lo] = from_float<T>(u * c - v * s);
     dst[swizzled ? kv_element_index(hi, pos, width, sizeof(T)) : hi] = from_float<T>(v * c + u * s);
@@ -101,6 +105,7 @@ ZB_API int zb_latent_rope(void* q_out, const float* q, long long q_stride, int q
   if (tokens < 0 || nh < 0 || rank <= 0 || rot < 0 || rot % 2 != 0 || page_size <= 0 || (rot > 0 && freqs == nullptr) ||
       (nh > 0 && (q == nullptr || q_out == nullptr)) || (cache != nullptr && (kv == nullptr || norm_w == nullptr)))
     return ERR_BAD_ARGUMENT;
+  if (rot > 2 * LR_MAX_HALF) return ERR_UNSUPPORTED;
   if (tokens == 0) return OK;
   LatentRopeArgs a;
   a.kv = kv; a.kv_stride = kv_stride; a.q = q; a.q_stride = q_stride; a.q_head_stride = q_head_stride;
@@ -108,9 +113,8 @@ ZB_API int zb_latent_rope(void* q_out, const float* q, long long q_stride, int q
   a.positions = positions; a.token_row = token_row; a.cache = cache; a.block_table = block_table;
   a.max_blocks = max_blocks; a.page_size = page_size; a.num_pages = num_pages; a.num_rows = num_rows; a.nh = nh;
   a.rank = rank; a.rot = rot; a.status = status;
-  const dim3 grid(tokens, (nh + 1 + LR_WARPS - 1) / LR_WARPS);
   auto s = static_cast<cudaStream_t>(stream);
-  if (dtype == DTYPE_F32) latent_rope_kernel<float><<<grid, LR_WARPS * 32, 0, s>>>(a);
-  else latent_rope_kernel<__nv_bfloat16><<<grid, LR_WARPS * 32, 0, s>>>(a);
+  if (dtype == DTYPE_F32) latent_rope_kernel<float><<<tokens, LR_THREADS, 0, s>>>(a);
+  else latent_rope_kernel<__nv_bfloat16><<<tokens, LR_THREADS, 0, s>>>(a);
   return launch_result();
 }

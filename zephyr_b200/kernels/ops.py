@@ -66,7 +66,7 @@ _SIGNATURES = {
                           c_void_p],
     "zb_store_last_token": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
     "zb_sum_rms_norm": [c_void_p, c_longlong, c_int, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_void_p,
-                        c_int, c_float, c_int, c_int, c_void_p],
+                        c_void_p, c_int, c_float, c_int, c_int, c_void_p],
     "zb_clamped_gate": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_float, c_float,
                         c_void_p],
     "zb_scale_rows": [c_void_p, c_longlong, c_float, c_void_p],
@@ -483,11 +483,14 @@ def pair_embedding(table: torch.Tensor, pair_table: torch.Tensor, ctx_ids: torch
 
 
 def sum_rms_norm(x: torch.Tensor, a: torch.Tensor | None, b: torch.Tensor | None, w: torch.Tensor | None,
-                 eps: float, out_dtype: torch.dtype | None = None) -> torch.Tensor | None:
-    """x (float32 [rows, H], unit inner stride, rows may be slices of wider rows) += (a + b) in place, where a
-    and b are contiguous [rows, H] summands of either type or None; then, with a scale ``w``, returns
+                 eps: float, out_dtype: torch.dtype | None = None, bias: torch.Tensor | None = None) -> torch.Tensor | None:
+    """x (float32 [rows, H], unit inner stride, rows may be slices of wider rows) += (a + b + bias) in place,
+    where a and b are contiguous [rows, H] summands of either type or None and ``bias`` is a float32 [H] shift
+    of one of them (added to every row), or None; then, with a scale ``w``, returns
     x / sqrt(mean(x^2) + eps) * w in ``out_dtype``.  Statistics and sums are float32."""
-    _cuda(x, a, b, w)
+    _cuda(x, a, b, w, bias)
+    _f32_vector(bias, x.shape[-1], "the shift")
+    _require(bias is None or a is not None or b is not None, "a shift comes with a summand")
     _require(x.dim() == 2 and x.dtype == torch.float32 and x.stride(1) == 1, "a float32 stream [rows, H]")
     rows, H = x.shape
     for summand in (a, b):
@@ -498,7 +501,7 @@ def sum_rms_norm(x: torch.Tensor, a: torch.Tensor | None, b: torch.Tensor | None
         out = torch.empty((rows, H), dtype=out_dtype or torch.float32, device=x.device)
     _check(library().zb_sum_rms_norm(_ptr(out), H, DTYPE_CODE[out.dtype] if out is not None else 0, _ptr(x), x.stride(0),
                                      _ptr(a), DTYPE_CODE[a.dtype] if a is not None else 0, _ptr(b),
-                                     DTYPE_CODE[b.dtype] if b is not None else 0, _ptr(w),
+                                     DTYPE_CODE[b.dtype] if b is not None else 0, _ptr(bias), _ptr(w),
                                      _scale_code(w, H) if w is not None else 0, float(eps), rows, H, _stream()),
            "sum_rms_norm")
     return out

@@ -14,6 +14,7 @@
     python -m zephyr_b200.kernels.timing decode_attention --softcap 30 | --keys-only --kv-heads 1
     python -m zephyr_b200.kernels.timing experts --tokens 2048 --hidden 2048 --ffn 1536 --experts 16 --top 4
     python -m zephyr_b200.kernels.timing head_linear --tokens 2048 --heads 16 --n 128 --k 128
+    python -m zephyr_b200.kernels.timing stream_parts --tokens 2048 --hidden 2048 --ffn 6144
 
 Each case rotates over several copies of its large operands, together larger than the L2 cache, so
 that a kernel bound by memory is timed against memory and not against L2.  Time is taken with CUDA
@@ -450,6 +451,83 @@ def norms(args) -> dict:
 CASES.update({"state_scan": state_scan, "conv_silu": conv_silu, "norms": norms})
 
 
+def stream_parts(args) -> dict:
+    """The small kernels of a design whose layers run mixer and feed-forward side by side on a float32 stream,
+    each beside its like: the sum of two summands + RMS norm beside sum + layer norm with a rounded sum and
+    beside the bfloat16 stream's sum + RMS norm; the bounded gate with biases on a float32 product beside
+    SiLU * up on a bfloat16 one; the latent's norm + rotation + cache write beside the latent's norm + cache
+    write alone; the hashed pair embedding beside the plain float32 one; routing by sigmoid scores limited
+    to groups beside softmax routing."""
+    device = torch.device("cuda")
+    T, H, I = (args.tokens or args.rows), args.hidden, args.ffn
+    bf = torch.bfloat16
+    out = {"tokens": T, "hidden": H, "ffn": I}
+    n = _copies(T * H * 14)
+    stream = [torch.randn((T, H), device=device) for _ in range(n)]
+    stream16 = [torch.randn((T, H), device=device, dtype=bf) for _ in range(n)]
+    a16 = [torch.randn((T, H), device=device, dtype=bf) for _ in range(n)]
+    b32 = [torch.randn((T, H), device=device) for _ in range(n)]
+    w = torch.ones(H, device=device, dtype=bf)
+    w32 = torch.ones(H, device=device)
+    us = _time(lambda i: ops.sum_rms_norm(stream[i % n], a16[i % n], a16[(i + 1) % n], w, 1e-6, bf), args.warmup, args.iters)
+    out["sum_rms_norm_two_bf16"] = {"us": round(us, 2), "gbs": round(T * H * 14 / us / 1e3, 1)}
+    us = _time(lambda i: ops.sum_rms_norm(stream[i % n], a16[i % n], b32[i % n], w, 1e-6, bf), args.warmup, args.iters)
+    out["sum_rms_norm_bf16_f32"] = {"us": round(us, 2), "gbs": round(T * H * 16 / us / 1e3, 1)}
+    us = _time(lambda i: ops.residual_layer_norm(stream[i % n], a16[i % n], w32, None, 1e-6, 1.0, rounded_sum=True),
+               args.warmup, args.iters)
+    out["like: residual_layer_norm_rounded_sum"] = {"us": round(us, 2), "gbs": round(T * H * 12 / us / 1e3, 1)}
+    us = _time(lambda i: ops.add_rmsnorm(stream16[i % n], a16[i % n], w, 1e-6), args.warmup, args.iters)
+    out["like: add_rmsnorm"] = {"us": round(us, 2), "gbs": round(T * H * 8 / us / 1e3, 1)}
+    m = _copies(T * I * 10)
+    gu32 = [torch.randn((T, 2 * I), device=device) for _ in range(m)]
+    gu16 = [torch.randn((T, 2 * I), device=device, dtype=bf) for _ in range(m)]
+    bias = torch.zeros(2 * I, device=device)
+    us = _time(lambda i: ops.clamped_gate(gu32[i % m], bias, 7.0, 1.702, 1.0, bf, blocked=True), args.warmup, args.iters)
+    out["clamped_gate_f32_in"] = {"us": round(us, 2), "gbs": round(T * I * 10 / us / 1e3, 1)}
+    us = _time(lambda i: ops.silu_mul(gu16[i % m], blocked=True), args.warmup, args.iters)
+    out["like: silu_mul_bf16_in"] = {"us": round(us, 2), "gbs": round(T * I * 6 / us / 1e3, 1)}
+    nh, rank, rot, dim = args.heads, args.head_dim - 32, 32, 128
+    width = rank + rot
+    pages = math.ceil(T / args.page_size) + 1
+    cache = torch.zeros((pages, args.page_size * width), device=device, dtype=bf)
+    table = torch.arange(1, pages, dtype=torch.int32, device=device).view(1, -1)
+    positions = torch.arange(T, dtype=torch.int32, device=device)
+    token_row = torch.zeros(T, dtype=torch.int32, device=device)
+    status = ops.new_status(device)
+    k = _copies(T * nh * (dim + rot) * 4)
+    q = [torch.randn((T, nh * (dim + rot)), device=device) for _ in range(k)]
+    kv = torch.randn((T, width), device=device)
+    q_out = torch.empty((T, nh * width), device=device, dtype=bf)
+    ones, freqs = torch.ones(rank, device=device), torch.rand(rot // 2, device=device)
+    us = _time(lambda i: ops.latent_rope(q[i % k], nh, dim + rot, dim, q_out, kv, rank, rot, ones, 1e-6, freqs, 1.2, positions,
+                                         token_row, cache, table, status, bf), args.warmup, args.iters)
+    moved = T * (nh * rot * 6 + width * 6)
+    out["latent_rope"] = {"heads": nh, "rank": rank, "rot": rot, "us": round(us, 2), "gbs": round(moved / us / 1e3, 1)}
+    ones_w = torch.ones(width, device=device)
+    us = _time(lambda i: ops.qkv_pairs(kv, 0, 1, width, 0, None, None, ones_w, 1e-6, None, 0, positions, token_row, cache, table,
+                                       status, bf), args.warmup, args.iters)
+    out["like: latent norm + cache write"] = {"us": round(us, 2), "gbs": round(T * width * 6 / us / 1e3, 1)}
+    V = 32768
+    table_e = torch.randn((V, H), device=device, dtype=bf)
+    pairs = torch.randn((65522, H), device=device, dtype=bf)
+    ids = torch.randint(0, V, (T,), dtype=torch.int32, device=device)
+    one = torch.zeros(1, dtype=torch.int32, device=device)
+    rows_len = torch.full((1,), T, dtype=torch.int32, device=device)
+    last = torch.zeros(4, dtype=torch.int32, device=device)
+    us = _time(lambda i: ops.pair_embedding(table_e, pairs, ids, positions, token_row, one, rows_len, one, last, 36313, 27191, status),
+               args.warmup, args.iters)
+    out["pair_embedding (two launches)"] = {"us": round(us, 2), "gbs": round(T * H * 8 / us / 1e3, 1)}
+    us = _time(lambda i: ops.embedding_f32(table_e, ids, status), args.warmup, args.iters)
+    out["like: embedding_f32"] = {"us": round(us, 2), "gbs": round(T * H * 6 / us / 1e3, 1)}
+    logits = torch.randn((T, args.experts), device=device)
+    us = _time(lambda i: ops.route(logits, None, args.top, "sigmoid", (4, 2, 2), 2.5), args.warmup, args.iters)
+    out["route_sigmoid_groups"] = {"experts": args.experts, "top": args.top, "us": round(us, 2)}
+    us = _time(lambda i: ops.route(logits, None, args.top), args.warmup, args.iters)
+    out["like: route_softmax"] = {"us": round(us, 2)}
+    ops.check_status(status, "stream_parts")
+    return out
+
+
 def experts(args) -> dict:
     """A routed feed-forward's products: ``--tokens`` tokens of width ``--hidden``, each taking ``--top`` of
     ``--experts`` experts of inner size ``--ffn`` (uniform random choices), routing excluded.  With few
@@ -487,7 +565,7 @@ def head_linear(args) -> dict:
             "tflops": round(flops / us / 1e6, 1), "gbs": round(moved / us / 1e3, 1)}
 
 
-CASES.update({"experts": experts, "head_linear": head_linear})
+CASES.update({"experts": experts, "head_linear": head_linear, "stream_parts": stream_parts})
 
 
 def main(argv=None) -> int:

@@ -161,6 +161,12 @@ class FeedForward(Part):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
 
+    def forward_summands(self, x: torch.Tensor) -> tuple[torch.Tensor, ...]:
+        """The output as summands whose sum it is: [T, hidden] tensors and at most one float32 [hidden] shift
+        for every row (a last bias left to whoever adds the output to the stream).  A block that adds the
+        output up in a kernel of its own asks for this."""
+        return (self.forward(x),)
+
     def as_gated_products(self) -> tuple[torch.Tensor, torch.Tensor] | None:
         """(gate_up weight [2I, hidden] in blocks of 8 gate rows and their 8 up rows, down weight
         [hidden, I]) if this part is down(silu(gate(x)) * up(x)); None otherwise."""
@@ -203,7 +209,8 @@ class ResidualStream:
     the stream had it at hand (an input part that writes both); it is void once anything is added."""
 
     hidden: torch.Tensor
-    pending: "torch.Tensor | tuple[torch.Tensor, ...] | None" = None    # a tuple: summands that are added to each other first
+    # a tuple: summands that are added to each other first; one of them may be a float32 [H] shift for every row
+    pending: "torch.Tensor | tuple[torch.Tensor, ...] | None" = None
     deferred: DeferredSum | None = None
     rounded: torch.Tensor | None = None
 

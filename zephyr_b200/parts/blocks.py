@@ -149,7 +149,7 @@ class ParallelResidual(Block):
         if self.feed_forward is None:
             stream.pending = (mixed,)
         else:
-            stream.pending = (mixed, self.feed_forward.forward(normed))
+            stream.pending = (mixed, *self.feed_forward.forward_summands(normed))
         return stream
 
 

@@ -126,7 +126,8 @@ class NormHead(OutputPart):
             stream.flush()
         rows = ops.gather_rows(stream.hidden, wanted, ctx.status)
         if isinstance(stream.pending, tuple):       # summands that are added to each other first, then to the stream
-            normed = self.norm.sum_forward(rows, tuple(ops.gather_rows(part, wanted, ctx.status) for part in stream.pending))
+            normed = self.norm.sum_forward(rows, tuple(ops.gather_rows(part, wanted, ctx.status) if part.dim() == 2 else part
+                                                       for part in stream.pending))
         elif stream.pending is not None:
             normed = self.norm.add_forward(rows, ops.gather_rows(stream.pending, wanted, ctx.status))
         else:

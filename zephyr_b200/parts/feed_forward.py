@@ -85,11 +85,18 @@ class SwiGLU(FeedForward):
         # The chain of small products has SiLU in its epilogue; another activation keeps the layer off it.
         return (self.w_gate_up, self.w_down) if self.blocked and self.activation == "silu" else None
 
+    def _bounded_hidden(self, x: torch.Tensor) -> torch.Tensor:
+        product = ops.linear(x, self.w_gate_up, out_dtype=torch.float32)
+        return ops.clamped_gate(product, self.b_gate_up, self.limit, self.alpha, self.up_shift, self.dtype, blocked=self.blocked)
+
+    def forward_summands(self, x: torch.Tensor) -> tuple[torch.Tensor, ...]:
+        if self.clamped and self.b_down is not None:      # the last bias joins the sum into the stream, in float32
+            return ops.linear(self._bounded_hidden(x), self.w_down), self.b_down
+        return (self.forward(x),)
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if self.clamped:
-            product = ops.linear(x, self.w_gate_up, out_dtype=torch.float32)
-            hidden = ops.clamped_gate(product, self.b_gate_up, self.limit, self.alpha, self.up_shift, self.dtype,
-                                      blocked=self.blocked)
+            hidden = self._bounded_hidden(x)
             if self.b_down is None:
                 return ops.linear(hidden, self.w_down)
             return ops.add_bias(ops.linear(hidden, self.w_down, out_dtype=torch.float32), self.b_down)

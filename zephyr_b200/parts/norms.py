@@ -35,13 +35,21 @@ class RMSNorm(Norm):
         return ops.rmsnorm(x, self.weight, self.eps)
 
     def sum_forward(self, stream: torch.Tensor, summands: tuple) -> torch.Tensor:
-        """stream (float32) += (the first summand + the second), in place and in float32; returns the norm
-        of the sum in the model's type.  One kernel for the sums and the norm."""
-        a = summands[0] if len(summands) > 0 else None
-        b = summands[1] if len(summands) > 1 else None
-        for more in summands[2:]:
+        """stream (float32) += (the summands added to each other), in place and in float32; returns the norm
+        of the sum in the model's type.  A summand is [rows, H], or a float32 [H] shift that goes on every
+        row.  Two summands and a shift take one kernel for the sums and the norm."""
+        rows = [s for s in summands if s.dim() == 2]
+        shifts = [s for s in summands if s.dim() == 1]
+        for more in rows[2:]:
             stream.add_(more)
-        return ops.sum_rms_norm(stream, a, b, self.weight, self.eps, out_dtype=self.dtype)
+        shift = None
+        if shifts and rows:
+            shift = shifts[0] if len(shifts) == 1 else torch.stack(shifts).sum(0)
+        elif shifts:
+            stream.add_(torch.stack(shifts).sum(0))
+        a = rows[0] if len(rows) > 0 else None
+        b = rows[1] if len(rows) > 1 else None
+        return ops.sum_rms_norm(stream, a, b, self.weight, self.eps, out_dtype=self.dtype, bias=shift)
 
     def add_forward(self, residual: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
         return ops.add_rmsnorm(residual, delta, self.weight, self.eps)
