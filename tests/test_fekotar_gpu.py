@@ -357,6 +357,65 @@ def test_bounded_gate(cuda_device, in_dtype, out_dtype, tokens, inner, blocked, 
     assert (out.cpu().double() - expected).abs().max() < bound * max(1.0, float(expected.abs().max()))
 
 
+def _bounded_feed_forward_case(tokens, width, inner, biased, limit, seed):
+    """x, gate and up weights (bfloat16 values), biases, and y = g * sigmoid(slope * g) * (u + 1) in float64."""
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(tokens, width, generator=g).bfloat16()
+    w_gate = (torch.randn(inner, width, generator=g) * 1.5 * width ** -0.5).bfloat16()
+    w_up = (torch.randn(inner, width, generator=g) * 1.5 * width ** -0.5).bfloat16()
+    b_gate, b_up = (torch.randn(inner, generator=g) * 0.5, torch.randn(inner, generator=g) * 0.5) if biased else (None, None)
+    gd = x.double() @ w_gate.double().T + (b_gate.double() if biased else 0.0)
+    ud = x.double() @ w_up.double().T + (b_up.double() if biased else 0.0)
+    gd, ud = gd.clamp(max=limit), ud.clamp(min=-limit, max=limit)
+    assert float((gd == limit).double().mean()) > 0.02 and float((ud.abs() == limit).double().mean()) > 0.02      # the bounds bite
+    return x, w_gate, w_up, b_gate, b_up, gd * torch.sigmoid(GATE_SLOPE * gd) * (ud + 1.0)
+
+
+@pytest.mark.parametrize("kernel,tokens,width,inner,biased,limit", [
+    ("few", 1, 64, 24, True, 1.0), ("few", 7, 200, 136, False, 0.7), ("few", 16, 1024, 512, True, 1.5),
+    ("many", 130, 64, 24, True, 1.0), ("many", 600, 200, 136, True, 0.7), ("many", 300, 96, 1000, False, 1.2),
+    ("many", 257, 512, 328, True, 2.0)])
+def test_bounded_gate_where_the_product_ends(cuda_device, kernel, tokens, width, inner, biased, limit):
+    """Biases, bounds and the gate inside the product's kernel: the weight streamer for few rows, tcgen05 for many,
+    with inner sizes that end inside a tile of columns and row counts that end inside a tile of rows."""
+    from zephyr_b200.kernels import ops
+
+    x, w_gate, w_up, b_gate, b_up, expected = _bounded_feed_forward_case(tokens, width, inner, biased, limit, tokens + inner)
+    packed = torch.stack([w_gate.view(-1, 8, width), w_up.view(-1, 8, width)], dim=1).reshape(-1, width).contiguous().to(cuda_device)
+    bias = torch.stack([b_gate.view(-1, 8), b_up.view(-1, 8)], dim=1).reshape(-1).contiguous().to(cuda_device) if biased else None
+    form = ops.BoundedGate(bias, limit, GATE_SLOPE, 1.0)
+    product = ops.gemm_small if kernel == "few" else ops.gemm_tc
+    out = product(x.to(cuda_device), packed, swiglu=True, bounded=form)
+    ops.check_status(ops.device_status(cuda_device))
+    assert out.shape == (tokens, inner) and out.dtype == torch.bfloat16
+    assert (out.cpu().double() - expected).abs().max() < 2.0 ** -7 * max(1.0, float(expected.abs().max()))
+
+
+@pytest.mark.parametrize("tokens", [3, 40, 520])
+@pytest.mark.parametrize("inner,biased", [(48, True), (50, True), (136, False)])
+def test_the_bounded_feed_forward_part_at_every_count_of_rows(cuda_device, tokens, inner, biased):
+    """The part picks a kernel by the number of rows; every choice computes the same function."""
+    from zephyr_b200.config.spec import FeedForwardSpec
+    from zephyr_b200.parts.base import FEED_FORWARDS
+
+    width, limit = 72, 0.9
+    x, w_gate, w_up, b_gate, b_up, hidden = _bounded_feed_forward_case(tokens, width, inner, biased, limit, 5 * tokens + inner)
+    g = torch.Generator().manual_seed(inner)
+    w_down = (torch.randn(width, inner, generator=g) * inner ** -0.5).bfloat16()
+    b_down = torch.randn(width, generator=g) * 0.5
+    names = {"gate_proj": "gate", "up_proj": "up", "down_proj": "down"}
+    weights = {"gate": w_gate, "up": w_up, "down": w_down}
+    if biased:
+        names.update({"gate_bias": "gate.b", "up_bias": "up.b", "down_bias": "down.b"})
+        weights.update({"gate.b": b_gate, "up.b": b_up, "down.b": b_down})
+    spec = FeedForwardSpec("gated", {"hidden_size": width, "intermediate_size": inner, "activation": "clamped_swish", "limit": limit,
+                                     "alpha": GATE_SLOPE, "up_shift": 1.0, **names})
+    part = FEED_FORWARDS["gated"](spec, {k: v.to(cuda_device) for k, v in weights.items()}, torch.bfloat16)
+    out = part.forward(x.to(cuda_device)).float().cpu().double()
+    expected = hidden @ w_down.double().T + (b_down.double() if biased else 0.0)
+    assert (out - expected).abs().max() < 2.0 ** -6 * max(1.0, float(expected.abs().max()))
+
+
 @pytest.mark.parametrize("experts,top,groups,scale", [(12, 2, (3, 2), 2.0), (8, 3, (4, 2), 1.5), (10, 2, (5, 3), 3.0), (12, 4, (2, 1), 0.8),
                                                       (9, 2, (3, 3), 1.0), (6, 1, None, 0.5), (4, 4, None, 2.5), (200, 8, (25, 4), 1.0),
                                                       (7, 7, (7, 7), 1.0), (16, 1, (16, 1), 1.0), (6, 3, (2, 1), 1.0)])

@@ -52,6 +52,38 @@ __device__ __forceinline__ float load_scale(const void* w, int w_dtype, int i) {
                               : __bfloat162float(static_cast<const __nv_bfloat16*>(w)[i]);
 }
 
+// What a gated feed-forward does with a gate sum G and its up sum U where a product's epilogue applies
+// it, in float32.  GATE_SILU: silu(G) * U.  GATE_RELU: max(G, 0) * U.  GATE_BOUNDED: with g = min(G + b_g,
+// limit) and u = clamp(U + b_u, -limit, limit), g * sigmoid(alpha * g) * (u + shift); `bias` holds one
+// float32 per row of the packed weight (b_g and b_u where their rows are), or is null.
+constexpr int GATE_SILU = 0;
+constexpr int GATE_RELU = 1;
+constexpr int GATE_BOUNDED = 2;
+
+struct GateForm {
+  int kind;
+  const float* bias;
+  float limit, alpha, shift;
+};
+
+inline GateForm plain_gate(int kind) { return GateForm{kind, nullptr, 0.0f, 1.0f, 0.0f}; }
+
+// The bounded gate from sums that already carry their biases.
+template <bool FAST>
+__device__ __forceinline__ float bounded_gate(float g, float u, const GateForm& f) {
+  g = fminf(g, f.limit);
+  u = fminf(fmaxf(u, -f.limit), f.limit);
+  float s;
+  if (FAST) {   // the special-function unit's exp2 and reciprocal: about 2^-21, far inside a bfloat16 rounding
+    float e;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(e) : "f"(-1.4426950408889634f * f.alpha * g));
+    asm("rcp.approx.ftz.f32 %0, %1;\n" : "=f"(s) : "f"(1.0f + e));
+  } else {
+    s = 1.0f / (1.0f + expf(-f.alpha * g));
+  }
+  return g * s * (u + f.shift);
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -33,7 +33,7 @@ struct SmallGemmArgs {
   const __nv_bfloat16* w;
   int M, N, K;
   long long ldx, ldw, ldy;
-  int relu_gate;      // with the gated epilogue: max(gate, 0) * up instead of silu(gate) * up
+  GateForm gate;      // with the gated epilogue: what becomes of a gate sum and its up sum
 };
 
 __device__ __forceinline__ uint4 load16_or_zero(const __nv_bfloat16* p, bool ok) {
@@ -123,9 +123,19 @@ gemm_small_kernel(const SmallGemmArgs a) {
             up += parts[c][w * PER_WARP + (mt * GS_ROWS + r + 8) * 8 + tok];
           }
         const int token = mt * 8 + tok, col = blockIdx.x * 8 + r;
-        if (token < a.M && n0 + r + 8 < a.N)
-          store_out<TOut>(y + static_cast<size_t>(token) * a.ldy + col,
-                          (a.relu_gate ? fmaxf(gate, 0.0f) : gate / (1.0f + expf(-gate))) * up);
+        if (token < a.M && n0 + r + 8 < a.N) {
+          float v;
+          if (a.gate.kind == GATE_BOUNDED) {
+            if (a.gate.bias != nullptr) {
+              gate += a.gate.bias[n0 + r];
+              up += a.gate.bias[n0 + r + 8];
+            }
+            v = bounded_gate<false>(gate, up, a.gate);
+          } else {
+            v = (a.gate.kind == GATE_RELU ? fmaxf(gate, 0.0f) : gate / (1.0f + expf(-gate))) * up;
+          }
+          store_out<TOut>(y + static_cast<size_t>(token) * a.ldy + col, v);
+        }
       }
     } else {
       for (int e = threadIdx.x; e < PER_WARP; e += GS_WARPS * 32) {
@@ -193,23 +203,39 @@ ZB_API int zb_gemm_small_ksplit(int N, int K) {
 // w holds gate and up rows interleaved in blocks of 8, y has N / 2 columns).
 // x: [M, K] bfloat16 rows ldx apart (ldx, ldw multiples of 8, pointers 16-byte aligned);
 // out_dtype: bfloat16 or float32.
-ZB_API int zb_gemm_small(void* y, const void* x, const void* w, int M, int N, int K, long long ldx, long long ldw,
-                         long long ldy, int out_dtype, int swiglu, void* stream) {
+static int small_gemm(void* y, const void* x, const void* w, int M, int N, int K, long long ldx, long long ldw,
+                      long long ldy, int out_dtype, bool gated, const GateForm& gate, void* stream) {
   if (!zb_gemm_small_supported(M, N, K)) return ERR_UNSUPPORTED;
   if (ldx < K || ldw < K || ldx % 8 != 0 || ldw % 8 != 0 || reinterpret_cast<uintptr_t>(x) % 16 != 0 ||
-      reinterpret_cast<uintptr_t>(w) % 16 != 0 || (swiglu && N % 16 != 0))
+      reinterpret_cast<uintptr_t>(w) % 16 != 0 || (gated && N % 16 != 0))
     return ERR_BAD_ARGUMENT;
   SmallGemmArgs a;
   a.y = y;
   a.x = static_cast<const __nv_bfloat16*>(x);
   a.w = static_cast<const __nv_bfloat16*>(w);
   a.M = M; a.N = N; a.K = K; a.ldx = ldx; a.ldw = ldw; a.ldy = ldy;
-  a.relu_gate = swiglu == 2;
+  a.gate = gate;
   const int ksplit = zb_gemm_small_ksplit(N, K);
   auto s = static_cast<cudaStream_t>(stream);
-  if (swiglu)
+  if (gated)
     return out_dtype == DTYPE_F32 ? small_gemm_dispatch<float, true>(a, ksplit, s)
                                   : small_gemm_dispatch<__nv_bfloat16, true>(a, ksplit, s);
   return out_dtype == DTYPE_F32 ? small_gemm_dispatch<float, false>(a, ksplit, s)
                                 : small_gemm_dispatch<__nv_bfloat16, false>(a, ksplit, s);
+}
+
+ZB_API int zb_gemm_small(void* y, const void* x, const void* w, int M, int N, int K, long long ldx, long long ldw,
+                         long long ldy, int out_dtype, int swiglu, void* stream) {
+  return small_gemm(y, x, w, M, N, K, ldx, ldw, ldy, out_dtype, swiglu != 0,
+                    plain_gate(swiglu == 2 ? GATE_RELU : GATE_SILU), stream);
+}
+
+// The gated form with the bounded gate: y[:, 8j + r] from the sums of w's rows 16j + r (gate) and 16j + 8 + r
+// (up), their biases (bias: float32 [N] in w's row order, or null), the bounds and the shifted product.
+ZB_API int zb_gemm_small_bounded(void* y, const void* x, const void* w, const float* bias, float limit, float alpha,
+                                 float shift, int M, int N, int K, long long ldx, long long ldw, long long ldy,
+                                 int out_dtype, void* stream) {
+  if (!(limit > 0.0f)) return ERR_BAD_ARGUMENT;
+  return small_gemm(y, x, w, M, N, K, ldx, ldw, ldy, out_dtype, true, GateForm{GATE_BOUNDED, bias, limit, alpha, shift},
+                    stream);
 }

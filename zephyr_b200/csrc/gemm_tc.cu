@@ -58,7 +58,7 @@ struct GemmTcArgs {
   CUtensorMap y_map;             // y as [M][N, or N / 2 with the activation]; box 64 x 32; rows and columns beyond are not written
   int M, N, K;
   int tiles_m, tiles;
-  int relu_gate;                 // with the gated epilogue: max(gate, 0) * up instead of silu(gate) * up
+  GateForm gate;                 // with the gated epilogue: what becomes of a gate sum and its up sum
   const int* tile_group;         // null, or per tile of 128 rows the matrix of w (rows group * N .. + N) its rows take;
                                  // a negative entry: the tile is not computed
   int groups;                    // matrices stacked in w (1 without tile_group)
@@ -109,7 +109,7 @@ __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wa
 // what lies beyond the matrix.
 template <int BN, int EPI>
 __device__ __forceinline__ void write_out_rows(const CUtensorMap& y_map, unsigned tmem_row, int row0, int n0, int width,
-                                               unsigned char* staging, int& stores, int lane, int relu_gate) {
+                                               unsigned char* staging, int& stores, int lane, const GateForm& form, int n_end) {
   // A group = 128 bytes of a row's output: 64 bfloat16 columns from two reads of 32 sums (four reads with
   // the activation, which halves them), or 32 float32 columns from one read.
   constexpr int READS = EPI == GT_EPI_SWIGLU ? 4 : EPI == GT_EPI_FLOAT ? 1 : 2;
@@ -138,13 +138,29 @@ __device__ __forceinline__ void write_out_rows(const CUtensorMap& y_map, unsigne
           w = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
         } else {
           float o[8];
+          if (EPI == GT_EPI_SWIGLU && form.kind == GATE_BOUNDED) {
+            // The biases of these 8 gate columns and their 8 up columns: the same for every lane, so the
+            // loads are broadcasts from L1.  Columns beyond the matrix take none; the store leaves them out.
+            float bias[16];
+            const int col = n0 + (group * READS + r) * 32 + 16 * j;
+            const bool biased = form.bias != nullptr && col < n_end;
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            if (EPI == GT_EPI_SWIGLU) {
-              const float gate = __uint_as_float(v[16 * j + i]), up = __uint_as_float(v[16 * j + 8 + i]);
-              o[i] = (relu_gate ? fmaxf(gate, 0.0f) : silu_fast(gate)) * up;
-            } else {
-              o[i] = __uint_as_float(v[8 * j + i]);
+            for (int i = 0; i < 4; ++i) {
+              const float4 b = biased ? __ldg(reinterpret_cast<const float4*>(form.bias + col) + i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+              bias[4 * i] = b.x; bias[4 * i + 1] = b.y; bias[4 * i + 2] = b.z; bias[4 * i + 3] = b.w;
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              o[i] = bounded_gate<true>(__uint_as_float(v[16 * j + i]) + bias[i], __uint_as_float(v[16 * j + 8 + i]) + bias[8 + i], form);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              if (EPI == GT_EPI_SWIGLU) {
+                const float gate = __uint_as_float(v[16 * j + i]), up = __uint_as_float(v[16 * j + 8 + i]);
+                o[i] = (form.kind == GATE_RELU ? fmaxf(gate, 0.0f) : silu_fast(gate)) * up;
+              } else {
+                o[i] = __uint_as_float(v[8 * j + i]);
+              }
             }
           }
           w.x = pack_bf16(o[0], o[1]);
@@ -273,7 +289,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1) gemm_tc_kernel(const __grid_con
       }
       tc_fence_after_sync();
       write_out_rows<BN, EPI>(a.y_map, tmem_base + (static_cast<unsigned>(32 * quarter) << 16) + acc * BN,
-                              m0 + 32 * quarter, n0, width, staging, stores, lane, a.relu_gate);
+                              m0 + 32 * quarter, n0, width, staging, stores, lane, a.gate, a.N);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) tc_mbar_arrive(&sh.acc_empty[acc]);
@@ -465,7 +481,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GT_THREADS, 1) gemm_
       }
       tc_fence_after_sync();
       write_out_rows<GP_BN, EPI>(a.y_map, tmem_base + (static_cast<unsigned>(32 * quarter) << 16) + acc * GP_BN,
-                                 m0 + 32 * quarter, n0, width, staging, stores, lane, a.relu_gate);
+                                 m0 + 32 * quarter, n0, width, staging, stores, lane, a.gate, a.N);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_in_cluster(in_cta_of_rank(smem_u32(&sh.acc_empty[acc]), 0));
@@ -566,11 +582,9 @@ ZB_API int zb_gemm_tc_supported(int M, int N, int K, long long ldx, int ldy, int
 // 1: y [M, N / 2] = silu(gate) * up for w's rows in
 // blocks of 8 gate rows and their 8 up rows; 3: the same with max(gate, 0) * up.  block_n is 256 or 128, or 2 for tiles of 256 x 256 on pairs of
 // SMs (0: chosen from the sizes).
-ZB_API int zb_gemm_tc(void* y, const void* x, const void* w, int M, int N, int K, long long ldx, int ldy, int epilogue,
-                      int block_n, int* status, void* stream) {
+static int gemm_tc_run(void* y, const void* x, const void* w, int M, int N, int K, long long ldx, int ldy, int epilogue,
+                       const GateForm& gate, int block_n, int* status, void* stream) {
   if (!zb_gemm_tc_supported(M, N, K, ldx, ldy, epilogue)) return ERR_UNSUPPORTED;
-  const int relu_gate = epilogue == GT_EPI_RELU_GATE;
-  if (relu_gate) epilogue = GT_EPI_SWIGLU;
   if (reinterpret_cast<uintptr_t>(y) % 16 != 0 || reinterpret_cast<uintptr_t>(x) % 16 != 0 ||
       reinterpret_cast<uintptr_t>(w) % 16 != 0)
     return ERR_BAD_ARGUMENT;
@@ -588,7 +602,7 @@ ZB_API int zb_gemm_tc(void* y, const void* x, const void* w, int M, int N, int K
   if (block_n != 256 && block_n != 128 && block_n != GT_PAIR) return ERR_BAD_ARGUMENT;
   GemmTcArgs a;
   a.M = M; a.N = N; a.K = K;
-  a.relu_gate = relu_gate;
+  a.gate = gate;
   a.tile_group = nullptr;
   a.groups = 1;
   a.status = status;
@@ -603,6 +617,24 @@ ZB_API int zb_gemm_tc(void* y, const void* x, const void* w, int M, int N, int K
   if (epilogue == GT_EPI_SWIGLU)
     return block_n == 256 ? gemm_tc_launch<256, GT_EPI_SWIGLU>(a, w, sms, s) : gemm_tc_launch<128, GT_EPI_SWIGLU>(a, w, sms, s);
   return block_n == 256 ? gemm_tc_launch<256, GT_EPI_PLAIN>(a, w, sms, s) : gemm_tc_launch<128, GT_EPI_PLAIN>(a, w, sms, s);
+}
+
+ZB_API int zb_gemm_tc(void* y, const void* x, const void* w, int M, int N, int K, long long ldx, int ldy, int epilogue,
+                      int block_n, int* status, void* stream) {
+  const bool relu = epilogue == GT_EPI_RELU_GATE;
+  return gemm_tc_run(y, x, w, M, N, K, ldx, ldy, relu ? GT_EPI_SWIGLU : epilogue, plain_gate(relu ? GATE_RELU : GATE_SILU),
+                     block_n, status, stream);
+}
+
+// The gated epilogue with the bounded gate: y [M, N / 2] bfloat16 from the float32 sums of w's gate and up
+// rows (blocks of 8 and 8), their biases (bias: float32 [N] in w's row order, 16-byte aligned, or null), the
+// bounds and the shifted product, rounded once.
+ZB_API int zb_gemm_tc_bounded(void* y, const void* x, const void* w, const float* bias, float limit, float alpha,
+                              float shift, int M, int N, int K, long long ldx, int ldy, int block_n, int* status,
+                              void* stream) {
+  if (!(limit > 0.0f) || reinterpret_cast<uintptr_t>(bias) % 16 != 0) return ERR_BAD_ARGUMENT;
+  return gemm_tc_run(y, x, w, M, N, K, ldx, ldy, GT_EPI_SWIGLU, GateForm{GATE_BOUNDED, bias, limit, alpha, shift}, block_n,
+                     status, stream);
 }
 
 // The same over several matrices stacked in w ([groups * N, K]): x [tiles_m * 128, K] is cut into tiles of
@@ -625,7 +657,7 @@ ZB_API int zb_gemm_tc_grouped(void* y, const void* x, const void* w, const int* 
     return ERR_CUDA;
   GemmTcArgs a;
   a.M = M; a.N = N; a.K = K;
-  a.relu_gate = relu_gate;
+  a.gate = plain_gate(relu_gate ? GATE_RELU : GATE_SILU);
   a.tile_group = tile_group;
   a.groups = groups;
   a.status = status;

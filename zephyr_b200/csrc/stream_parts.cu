@@ -207,44 +207,45 @@ sum_rms_norm_vec_kernel(OUT* out, long long out_stride, float* x, long long x_st
 }
 
 // -------------------------------------------------------------------------------------- clamped gate
-// Eight outputs a thread and step: I a multiple of 8 and every base aligned for eight values.
+// One 16-byte load of gates and one of ups a thread and step (four outputs from float32 sums, eight from
+// bfloat16): a warp's loads cover whole 32-byte sectors in either column order.  I a multiple of 8 and every
+// base aligned to 16 bytes.
 template <typename IN, typename OUT>
 __global__ void __launch_bounds__(256)
 clamped_gate_vec_kernel(OUT* out, const IN* gu, const float* bias, int T, int I, int blocked, float limit,
                         float alpha, float shift) {
-  // A CTA walks rows, a thread pieces of eight outputs of its row: no division, and a row's pieces are neighbours.
-  const int per_row = I / 8;
+  constexpr int PIECE = 16 / sizeof(IN);
+  // A CTA walks rows, a thread pieces of its row: no division, and a row's pieces are neighbours.
+  const int per_row = I / PIECE;
+  const GateForm form{GATE_BOUNDED, bias, limit, alpha, shift};
   for (long long t = blockIdx.x; t < T; t += gridDim.x)
   for (int j = threadIdx.x; j < per_row; j += blockDim.x) {
-    const int gi = blocked ? 16 * j : 8 * j;
-    const int ui = blocked ? gi + 8 : I + 8 * j;
+    const int o0 = PIECE * j;
+    const int gi = blocked ? (o0 >> 3) * 16 + (o0 & 7) : o0;
+    const int ui = blocked ? gi + 8 : I + o0;
     const IN* row = gu + t * 2 * I;
-    float g[8], u[8];
+    float g[PIECE], u[PIECE];
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
+    for (int h = 0; h < PIECE / 4; ++h) {
       const float4 gv = load4(row + gi + 4 * h), uv = load4(row + ui + 4 * h);
       g[4 * h] = gv.x; g[4 * h + 1] = gv.y; g[4 * h + 2] = gv.z; g[4 * h + 3] = gv.w;
       u[4 * h] = uv.x; u[4 * h + 1] = uv.y; u[4 * h + 2] = uv.z; u[4 * h + 3] = uv.w;
     }
     if (bias != nullptr) {
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
+      for (int h = 0; h < PIECE / 4; ++h) {
         const float4 gb = load4(bias + gi + 4 * h), ub = load4(bias + ui + 4 * h);
         g[4 * h] += gb.x; g[4 * h + 1] += gb.y; g[4 * h + 2] += gb.z; g[4 * h + 3] += gb.w;
         u[4 * h] += ub.x; u[4 * h + 1] += ub.y; u[4 * h + 2] += ub.z; u[4 * h + 3] += ub.w;
       }
     }
-    float y[8];
+    float y[PIECE];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      float gg = g[e], uu = u[e];
-      gg = fminf(gg, limit);
-      uu = fminf(fmaxf(uu, -limit), limit);
-      y[e] = gg / (1.0f + (sizeof(OUT) == 4 ? expf(-alpha * gg) : __expf(-alpha * gg))) * (uu + shift);   // the fast exponential's 2^-21 vanishes in a bfloat16 result
-    }
-    OUT* dst = out + t * I + 8 * j;
-    store4(dst, make_float4(y[0], y[1], y[2], y[3]));
-    store4(dst + 4, make_float4(y[4], y[5], y[6], y[7]));
+    for (int e = 0; e < PIECE; ++e)      // the fast exponential's 2^-21 vanishes in a bfloat16 result
+      y[e] = sizeof(OUT) == 4 ? bounded_gate<false>(g[e], u[e], form) : bounded_gate<true>(g[e], u[e], form);
+    OUT* dst = out + t * I + o0;
+#pragma unroll
+    for (int h = 0; h < PIECE / 4; ++h) store4(dst + 4 * h, make_float4(y[4 * h], y[4 * h + 1], y[4 * h + 2], y[4 * h + 3]));
   }
 }
 
@@ -375,7 +376,7 @@ ZB_API int zb_clamped_gate(void* out, int out_dtype, const void* gu, int in_dtyp
   using bf16 = __nv_bfloat16;
   if (I % 8 == 0 && reinterpret_cast<uintptr_t>(gu) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0 &&
       reinterpret_cast<uintptr_t>(bias) % 16 == 0) {
-    int threads = (I / 8 + 31) / 32 * 32;
+    int threads = (I / (in_dtype == DTYPE_F32 ? 4 : 8) + 31) / 32 * 32;
     threads = threads > 256 ? 256 : threads;
     const int blocks8 = T < 148 * 32 ? T : 148 * 32;
     if (out_dtype == DTYPE_F32)

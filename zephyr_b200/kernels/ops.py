@@ -146,6 +146,10 @@ _SIGNATURES = {
     "zb_fill_normal": [c_void_p, c_longlong, ctypes.c_ulonglong, c_float, c_float, c_int, c_void_p],
     "zb_gemm_tc_supported": [c_int, c_int, c_int, c_longlong, c_int, c_int],
     "zb_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_int, c_int, c_int, c_void_p, c_void_p],
+    "zb_gemm_tc_bounded": [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float, c_float, c_int, c_int, c_int, c_longlong,
+                           c_int, c_int, c_void_p, c_void_p],
+    "zb_gemm_small_bounded": [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float, c_float, c_int, c_int, c_int,
+                              c_longlong, c_longlong, c_longlong, c_int, c_void_p],
     "zb_gemm_nt_simt": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong,
                         c_int, c_int, c_void_p],
     "zb_fused_chain_stage_supported": [c_int, c_int, c_int, c_int, c_int],
@@ -1158,11 +1162,28 @@ def gemm_small_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
             and bool(library().zb_gemm_small_supported(x.shape[0], w.shape[0], x.shape[1])))
 
 
+@dataclass(frozen=True)
+class BoundedGate:
+    """The bounded gate as a product's epilogue: with g = min(G + b_g, limit) and u = clamp(U + b_u, -limit,
+    limit), g * sigmoid(alpha * g) * (u + shift).  ``bias`` is float32, one value per row of the packed weight
+    (b_g and b_u where their rows are), or None."""
+    bias: torch.Tensor | None
+    limit: float
+    alpha: float
+    shift: float
+
+
+def _bounded_args(bounded: BoundedGate, rows: int) -> tuple:
+    _require(bounded.limit > 0.0, "the bounded gate needs a positive limit")
+    _f32_vector(bounded.bias, rows, "the gate's bias")
+    return _ptr(bounded.bias), float(bounded.limit), float(bounded.alpha), float(bounded.shift)
+
+
 def gemm_small(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None,
-               swiglu: bool = False, act: str = "silu") -> torch.Tensor:
+               swiglu: bool = False, act: str = "silu", bounded: BoundedGate | None = None) -> torch.Tensor:
     """x [M <= 64, K] times w [N, K] transposed, bfloat16, float32 accumulation, weights read once.
     With ``swiglu`` the rows of w are blocks of 8 gate rows each followed by its 8 up rows, and the
-    result is silu(gate) * up, [M, N / 2]."""
+    result is silu(gate) * up, [M, N / 2]; with ``bounded`` as well, the bounded gate of those sums."""
     _cuda(x, w)
     _require(x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1], "x [M, K] and w [N, K]")
     _require(gemm_small_supported(x, w), "gemm_small takes bfloat16, M <= 64, K a multiple of 8, 16-byte aligned rows")
@@ -1171,6 +1192,12 @@ def gemm_small(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None =
     N = w.shape[0]
     _require(not swiglu or N % 16 == 0, "swiglu needs a multiple of 16 rows")
     out = torch.empty((M, N // 2 if swiglu else N), dtype=out_dtype, device=x.device)
+    if bounded is not None:
+        _require(swiglu, "the bounded gate is a gated epilogue")
+        _cuda(bounded.bias)
+        _check(library().zb_gemm_small_bounded(_ptr(out), _ptr(x), _ptr(w), *_bounded_args(bounded, N), M, N, K, x.stride(0),
+                                               w.stride(0), out.stride(0), DTYPE_CODE[out_dtype], _stream()), "gemm_small")
+        return out
     _check(library().zb_gemm_small(_ptr(out), _ptr(x), _ptr(w), M, N, K, x.stride(0), w.stride(0), out.stride(0),
                                    DTYPE_CODE[out_dtype], (2 if act == "relu" else 1) if swiglu else 0, _stream()),
            "gemm_small")
@@ -1194,11 +1221,13 @@ def gemm_tc_supported(x: torch.Tensor, w: torch.Tensor, swiglu: bool = False) ->
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, swiglu: bool = False, block_n: int = 0,
-            status: torch.Tensor | None = None, out_dtype: torch.dtype | None = None, act: str = "silu") -> torch.Tensor:
+            status: torch.Tensor | None = None, out_dtype: torch.dtype | None = None, act: str = "silu",
+            bounded: BoundedGate | None = None) -> torch.Tensor:
     """x [M, K] times w [N, K] transposed on tcgen05 tensor cores, bfloat16 with float32 sums in
     tensor memory; the result in bfloat16, or with ``out_dtype=torch.float32`` the sums as they are.
     With ``swiglu`` the rows of w are blocks of 8 gate rows each followed by its 8 up
-    rows, and the result is silu(gate) * up, [M, N / 2], taken from the float32 sums and rounded once.
+    rows, and the result is silu(gate) * up, [M, N / 2], taken from the float32 sums and rounded once
+    (with ``bounded`` as well: the bounded gate of those sums and their biases).
     ``block_n`` is the width of an output tile (256, 128; 2: tiles of 256 x 256 on pairs of SMs; 0: chosen).  ``status`` (default: the
     device's status word) receives a report if a wait inside the kernel ran out."""
     _cuda(x, w)
@@ -1213,6 +1242,12 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, swiglu: bool = False, block_n: int
     out = torch.empty((M, ldy), dtype=torch.float32 if wide else torch.bfloat16, device=x.device)
     if status is None:
         status = device_status(x.device)
+    if bounded is not None:
+        _require(swiglu, "the bounded gate is a gated epilogue")
+        _cuda(bounded.bias)
+        _check(library().zb_gemm_tc_bounded(_ptr(out), _ptr(x), _ptr(w), *_bounded_args(bounded, N), M, N, K, x.stride(0), ldy,
+                                            int(block_n), _ptr(status), _stream()), "gemm_tc")
+        return out if ldy == width else out[:, :width].contiguous()
     _require(act in ACTIVATIONS, f"the gate's activation is one of {sorted(ACTIVATIONS)}")
     gated = 3 if act == "relu" else 1         # the kernel's codes for the two gated epilogues
     _check(library().zb_gemm_tc(_ptr(out), _ptr(x), _ptr(w), M, N, K, x.stride(0), ldy, 2 if wide else (gated if swiglu else 0),

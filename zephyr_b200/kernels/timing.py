@@ -486,6 +486,19 @@ def stream_parts(args) -> dict:
     out["clamped_gate_f32_in"] = {"us": round(us, 2), "gbs": round(T * I * 10 / us / 1e3, 1)}
     us = _time(lambda i: ops.silu_mul(gu16[i % m], blocked=True), args.warmup, args.iters)
     out["like: silu_mul_bf16_in"] = {"us": round(us, 2), "gbs": round(T * I * 6 / us / 1e3, 1)}
+    # The same gate where the gate/up product ends: the weight streamer for a step's few rows (bound by the
+    # weight's bytes), tcgen05 for a prompt's many (bound by the products), each beside SiLU * up in that place.
+    form = ops.BoundedGate(bias, 7.0, 1.702, 1.0)
+    c = _copies(2 * I * H * 2)
+    packed = [torch.randn((2 * I, H), device=device, dtype=bf) * H ** -0.5 for _ in range(c)]
+    few = torch.randn((8, H), device=device, dtype=bf)
+    for name, extra in (("bounded", {"bounded": form}), ("like: silu", {})):
+        us = _time(lambda i: ops.gemm_small(few, packed[i % c], swiglu=True, **extra), args.warmup, args.iters)
+        out[f"gate_up_8_rows, {name}"] = {"us": round(us, 2), "gbs": round(2 * I * H * 2 / us / 1e3, 1)}
+    if T >= 128 and ops.gemm_tc_supported(stream16[0], packed[0], swiglu=True):
+        for name, extra in (("bounded", {"bounded": form}), ("like: silu", {})):
+            us = _time(lambda i: ops.gemm_tc(stream16[i % n], packed[i % c], swiglu=True, **extra), args.warmup, args.iters)
+            out[f"gate_up_{T}_rows, {name}"] = {"us": round(us, 2), "tflops": round(2 * T * 2 * I * H / us / 1e6, 1)}
     nh, rank, rot, dim = args.heads, args.head_dim - 32, 32, 128
     width = rank + rot
     pages = math.ceil(T / args.page_size) + 1

@@ -3,8 +3,9 @@ the spec's ``activation`` says "relu".
 
 ``activation`` "clamped_swish" is the bounded form, with biases on all three products where the spec names
 them: g = min(gate(x), limit), u = clamp(up(x), -limit, limit), y = g * sigmoid(alpha * g) * (u + up_shift),
-out = down(y).  Biases, bounds and the activation are one float32 pass over the unrounded product; the
-down product's bias joins its float32 sums, and the part then hands out float32.
+out = down(y).  Biases, bounds and the activation act on the product's unrounded float32 sums, inside the
+product's kernel for few rows and for many (one pass over the float32 product otherwise); the down product's
+bias joins the float32 sum into the stream.
 
 Gate and up run as one product over one packed weight [2I, H], as the reference packs them at
 load (src/layer/mlp.cpp:16-36); the reference puts all gate rows first, this part alternates blocks
@@ -86,6 +87,16 @@ class SwiGLU(FeedForward):
         return (self.w_gate_up, self.w_down) if self.blocked and self.activation == "silu" else None
 
     def _bounded_hidden(self, x: torch.Tensor) -> torch.Tensor:
+        # Biases, bounds and the gate where the products' float32 sums leave the tensor cores: a decode step's
+        # few rows on the weight streamer, a prompt's many on tcgen05; what lies between, and float32, takes
+        # the library's product and one pass over its unrounded result.
+        if self.blocked and x.dtype == torch.bfloat16:
+            bounded = ops.BoundedGate(self.b_gate_up, self.limit, self.alpha, self.up_shift)
+            if x.shape[0] <= ops.SMALL_GEMM_ROWS and ops.gemm_small_supported(x, self.w_gate_up):
+                return ops.gemm_small(x, self.w_gate_up, swiglu=True, bounded=bounded)
+            if ((x.shape[0] >= ops.GEMM_TC_MIN_ROWS or not ops.USE_LIBRARY_PRODUCTS)
+                    and ops.gemm_tc_supported(x, self.w_gate_up, swiglu=True)):
+                return ops.gemm_tc(x, self.w_gate_up, swiglu=True, bounded=bounded)
         product = ops.linear(x, self.w_gate_up, out_dtype=torch.float32)
         return ops.clamped_gate(product, self.b_gate_up, self.limit, self.alpha, self.up_shift, self.dtype, blocked=self.blocked)
 
