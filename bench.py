@@ -85,8 +85,8 @@ def kernel_fractions(config, batch: int, context: int, peak: dict) -> tuple[dict
     from zephyr_b200.kernels import timing
 
     base = dict(warmup=3, iters=20, heads=config.num_attention_heads, kv_heads=config.num_key_value_heads,
-                head_dim=config.head_dim, page_size=PAGE_SIZE, window=0, split=0, hidden=config.hidden_size,
-                ffn=config.intermediate_size)
+                head_dim=config.head_dim, page_size=PAGE_SIZE, window=0, split=0, softcap=0.0, keys_only=False,
+                hidden=config.hidden_size, ffn=config.intermediate_size)
     chain = timing.fused_chain(SimpleNamespace(rows=batch, **base))
     attention = timing.decode_attention(SimpleNamespace(batch=batch, context=context, **base))
     head = timing.gemm_small(SimpleNamespace(rows=batch, n=config.vocab_size, k=config.hidden_size, swiglu=False,
