@@ -204,6 +204,41 @@ def test_long_decoding(folders, cuda_device, dtype):
                           f"{name} long decoding")
 
 
+LONG = {"architecture": "Fekotar", "vocab": 90, "width": 128, "logit_scale": 0.5, "norm": {"eps": 1e-6},
+        "embedding": {"bigram": {"buckets": 61, "mul_prev": 13, "mul_cur": 5}},
+        "layers": [latent(8, 32, 32, 24, 96, 40, 0.12, dense(192, 1.0), base=1000.0, scaling=yarn(2.0, 128, 16.0, 1.0)),
+                   latent(4, 16, 16, 32, 144, 24, 0.1, moe(8, 2, 64, scale=1.5, groups=(4, 2)), base=5000.0),
+                   latent(16, 24, 64, 16, 64, 64, 0.1, moe(6, 3, 40, scale=0.7), base=300.0, scaling=yarn(4.0, 64, 8.0, 2.0))]}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_prompts_of_many_hundred_tokens(tmp_path, cuda_device, dtype):
+    """Portions of more than 512 tokens (from where the products with many rows and the grouped products of a
+    routed layer run on the tensor cores' own kernels in bfloat16) beside short ones: a prompt of 700 tokens
+    whole, the same in portions of 530, 2 and 168, and a second one of 600 that comes in beside decoded
+    tokens of the first."""
+    config = LONG if dtype == "float32" else without_choice(LONG)
+    folder = write_model(tmp_path / "long", config, seed=77, dtype=DTYPES[dtype])
+    requests = {"a": random_tokens(90, 712, seed=1), "b": random_tokens(90, 712, seed=2), "c": random_tokens(90, 606, seed=3)}
+    every = lambda lo, hi: list(range(0, hi - lo, 37)) + [hi - lo - 1]
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": requests["a"][:700], "want": every(0, 700)}], "end": []},
+             {"step": 1, "entries": [{"id": "b", "tokens": requests["b"][:530], "want": every(0, 530)}], "end": []},
+             {"step": 2, "entries": [{"id": "b", "tokens": requests["b"][530:532], "want": [0, 1]},
+                                     {"id": "a", "tokens": requests["a"][700:701], "want": [0]}], "end": []},
+             {"step": 3, "entries": [{"id": "a", "tokens": requests["a"][701:702], "want": [0]},
+                                     {"id": "c", "tokens": requests["c"][:600], "want": every(0, 600)},
+                                     {"id": "b", "tokens": requests["b"][532:700], "want": every(532, 700)}], "end": []}]
+    for i in range(6):
+        steps.append({"step": 4 + i, "entries": [{"id": "a", "tokens": [requests["a"][702 + i]], "want": [0]},
+                                                 {"id": "c", "tokens": [requests["c"][600 + i]], "want": [0]},
+                                                 {"id": "b", "tokens": [requests["b"][700 + i]], "want": [0]}],
+                      "end": ["a", "b", "c"] if i == 5 else []})
+    requests = {"a": requests["a"][:708], "b": requests["b"][:706], "c": requests["c"][:606]}
+    rows = collect(steps, replay(folder, dtype, steps, 32))
+    assert len(rows) > 60
+    assert_rows_match(rows, requests, folder, dtype, "long prompts")
+
+
 @pytest.mark.parametrize("name,dtype", [("A", "float32"), ("C", "bfloat16"), ("B", "float32"), ("mixer", "bfloat16")])
 def test_greedy_generation_through_the_engine(folders, cuda_device, name, dtype):
     from zephyr_b200 import Engine
@@ -478,7 +513,8 @@ def test_products_per_head_on_slices_of_wider_heads(cuda_device, x_dtype, w_dtyp
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("rank,rot,heads,page,scaling", [(40, 8, 3, 16, yarn(4.0, 64, 8.0, 2.0)), (96, 32, 8, 16, yarn(8.0, 128, 16.0, 1.0)),
                                                          (28, 4, 6, 16, None), (64, 64, 16, 32, yarn(2.0, 16, 2.0, 0.25)),
-                                                         (128, 32, 4, 32, None), (30, 2, 1, 16, None), (48, 16, 20, 16, yarn(3.0, 50, 5.0, 1.0))])
+                                                         (128, 32, 4, 32, None), (30, 2, 1, 16, None), (48, 16, 20, 16, yarn(3.0, 50, 5.0, 1.0)),
+                                                         (512, 64, 2, 16, yarn(4.0, 64, 8.0, 1.0)), (700, 68, 1, 32, None)])
 def test_attention_over_a_latent_with_a_rotated_part(cuda_device, dtype, rank, rot, heads, page, scaling):
     """The cached row is the normed latent followed by the rotated key part; queries carry the same two
     pieces.  Queries of head 0 point at one row each THROUGH THE ROTATED PART ONLY (the latent part of those

@@ -822,11 +822,11 @@ def test_kernels_refuse_what_they_do_not_take(ops, cuda_device):
     assert not ops.paged_decode_supported(16, 8, 128, torch.float32)
     assert not ops.paged_decode_supported(34, 2, 128, torch.bfloat16)     # 17 heads per group
     assert not ops.paged_decode_supported(4, 2, 48, torch.bfloat16)
-    q = torch.zeros((1, 2 * 520), device=cuda_device)                     # the general kernel takes widths up to 512
-    cache = torch.zeros((3, 2, 2, 4, 520), device=cuda_device)
+    q = torch.zeros((1, 2 * 776), device=cuda_device)                     # the general kernel takes widths up to 768
+    cache = torch.zeros((3, 2, 2, 4, 776), device=cuda_device)
     z = torch.zeros(1, dtype=torch.int32, device=cuda_device)
     with pytest.raises(ops.KernelError, match="does not support"):
-        ops.paged_attention(q, cache, z.view(1, 1), z, z, 1, z, z, z, 2, 2, 520, 0, 1.0, ops.new_status(cuda_device))
+        ops.paged_attention(q, cache, z.view(1, 1), z, z, 1, z, z, z, 2, 2, 776, 0, 1.0, ops.new_status(cuda_device))
     with pytest.raises(ops.KernelError):
         ops.rmsnorm(torch.zeros(4, 4), torch.ones(4), 1e-6)               # CPU tensors: no CPU path
 

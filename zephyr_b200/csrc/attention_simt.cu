@@ -1,7 +1,7 @@
 // Paged causal attention on CUDA cores, float32 arithmetic throughout: the kernel of the true
-// 32-bit path, and the general one (any head size up to 512, any head and group
-// counts, any page size, with or without a window, any mixture of prompt portions and single
-// decoded tokens).
+// 32-bit path, and the general one (any head size up to 512, and up to 768 where the keys are the
+// values too; any head and group counts, any page size, with or without a window, any mixture of
+// prompt portions and single decoded tokens).
 //
 // Math (reference: deps/ttl/src/kernels/attention/attention.cu:46-56,76-77,90-166): query head j
 // uses key/value head j / g; s = scale * (q . k) with scale = 1/sqrt(hd); a query at absolute
@@ -223,6 +223,7 @@ int attention_simt_launch(const AttentionArgs& a, int n_tiles, int head_chunks, 
   const size_t smem = static_cast<size_t>(ATT_MAX_PAIRS) * a.kd * sizeof(float) +
                       static_cast<size_t>(ATT_TILE) * (a.kd + (a.shared_kv ? 0 : a.vd) + KPad<T>::N) * sizeof(T);
   auto kernel = paged_attention_simt_kernel<T, ACC>;
+  if (smem > 227 * 1024) return ERR_UNSUPPORTED;      // (float32 keys and values of more than 512 each)
   if (smem > 48 * 1024 &&
       cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
     return ERR_CUDA;
@@ -244,6 +245,8 @@ int attention_simt_dispatch(const AttentionArgs& a, int n_tiles, int head_chunks
     case 9: case 10: return attention_simt_launch<T, 10>(a, n_tiles, head_chunks, stream);
     case 11: case 12: return attention_simt_launch<T, 12>(a, n_tiles, head_chunks, stream);
     case 13: case 14: case 15: case 16: return attention_simt_launch<T, 16>(a, n_tiles, head_chunks, stream);
+    case 17: case 18: case 19: case 20: return attention_simt_launch<T, 20>(a, n_tiles, head_chunks, stream);
+    case 21: case 22: case 23: case 24: return attention_simt_launch<T, 24>(a, n_tiles, head_chunks, stream);
     default: return ERR_UNSUPPORTED;
   }
 }
@@ -271,7 +274,7 @@ ZB_API int zb_paged_attention_simt(void* out, const void* q, const void* kv_cach
   if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || kd <= 0 || vd <= 0 || page_size <= 0 || n_tiles < 0 || window < 0 ||
       chunk < 0 || softcap < 0.0f || (shared_kv && kd != vd))
     return ERR_BAD_ARGUMENT;
-  if (kd > 512 || vd > 512) return ERR_UNSUPPORTED;
+  if (kd > 768 || vd > 768) return ERR_UNSUPPORTED;
   if (n_tiles == 0) return OK;
   const int g = nh / nkv;
   const int heads_per_chunk = g < ATT_MAX_PAIRS ? g : ATT_MAX_PAIRS;

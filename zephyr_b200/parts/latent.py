@@ -54,8 +54,8 @@ class LatentAttention(Mixer):
             raise ConfigError("latent attention needs positive head count, head sizes and rank")
         self.rot = int(p.get("rot_dim", 0))
         self.kw = self.rank + self.rot            # what a position keeps: the latent and the rotated key part
-        if self.kw > 512:
-            raise ConfigError(f"latent attention keeps at most 512 values a position, not {self.kw}")
+        if self.kw > 768:
+            raise ConfigError(f"latent attention keeps at most 768 values a position, not {self.kw}")
         self.position = None
         self.freqs, self.rope_mult = None, 1.0
         if self.rot > 0:
