@@ -63,6 +63,8 @@ GEFOVIK_SIZES = {
 # turn.  A position keeps kv_rank + rot_dim = 128 values.  Beside it runs Gefovik, the closest design the
 # engine has, with latent attention over a latent of 128 in every layer and the same feed-forward sizes.
 FEKOTAR_SIZES = {
+    "w1024": dict(width=1024, ff=3072, layers=8, heads=8, dim=128, rot_dim=32, vdim=128, kv_rank=96, q_rank=384, experts=16, top=4,
+                  groups=(4, 2)),
     "w2048": dict(width=2048, ff=6144, layers=8, heads=16, dim=128, rot_dim=32, vdim=128, kv_rank=96, q_rank=768, experts=16, top=4,
                   groups=(4, 2)),
     "w4096": dict(width=4096, ff=12288, layers=8, heads=16, dim=128, rot_dim=32, vdim=128, kv_rank=96, q_rank=1536, experts=16, top=4,
