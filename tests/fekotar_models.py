@@ -51,7 +51,7 @@ CONFIGS = {
     # no multiple of eight, a bound that cuts most values
     "B": {"architecture": "Fekotar", "vocab": 131, "width": 96, "logit_scale": 1.0, "norm": {"eps": 1e-6}, "layers": [
         latent(8, 24, 32, 16, 96, 40, 0.2, moe(9, 2, 36, scale=1.0, groups=(3, 3)), base=2000.0, scaling=yarn(8.0, 128, 16.0, 1.0)),
-        latent(5, 32, 16, 32, 48, 64, 0.15, dense(50, 0.5), base=50000.0),
+        latent(5, 32, 16, 32, 48, 64, 0.15, dense(50, 0.5), base=70000.0),
         latent(2, 40, 8, 20, 56, 8, 0.3, moe(4, 4, 20, scale=2.5))]},
     # C: pages of 32, sixteen heads on a cached row of 128, a row of 160, one group kept of two, one value a head
     "C": {"architecture": "Fekotar", "vocab": 64, "width": 128, "logit_scale": 2.0, "norm": {"eps": 1e-6},

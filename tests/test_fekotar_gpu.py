@@ -451,7 +451,7 @@ def test_the_bounded_feed_forward_part_at_every_count_of_rows(cuda_device, token
     assert (out - expected).abs().max() < 2.0 ** -6 * max(1.0, float(expected.abs().max()))
 
 
-@pytest.mark.parametrize("experts,top,groups,scale", [(12, 2, (3, 2), 2.0), (8, 3, (4, 2), 1.5), (10, 2, (5, 3), 3.0), (12, 4, (2, 1), 0.8),
+@pytest.mark.parametrize("experts,top,groups,scale", [(15, 2, (3, 2), 1.75), (8, 3, (4, 2), 1.5), (10, 2, (5, 3), 3.0), (12, 4, (2, 1), 0.8),
                                                       (9, 2, (3, 3), 1.0), (6, 1, None, 0.5), (4, 4, None, 2.5), (200, 8, (25, 4), 1.0),
                                                       (7, 7, (7, 7), 1.0), (16, 1, (16, 1), 1.0), (6, 3, (2, 1), 1.0)])
 def test_sigmoid_routing_limited_to_groups(cuda_device, experts, top, groups, scale):

@@ -42,7 +42,7 @@ def draw_config(seed: int) -> dict:
         if rot and rng.random() < 0.7:
             original = rng.choice([16, 32, 64, 512])
             scaling = yarn(rng.choice([1.5, 2.0, 4.0, 8.0]), original, rng.choice([32.0, 8.0, 4.0]), rng.choice([1.0, 0.5, 2.0]))
-        return rank, rot, scaling, rng.choice([20.0, 500.0, 10000.0, 50000.0])
+        return rank, rot, scaling, rng.choice([20.0, 500.0, 10000.0, 80000.0])
 
     layers = []
     for _ in range(rng.randint(1, 6)):
@@ -53,8 +53,8 @@ def draw_config(seed: int) -> dict:
     config = {"architecture": "Fekotar", "vocab": rng.randint(50, 700), "width": width,
               "logit_scale": rng.choice([0.25, 0.5, 1.0, 3.0]), "norm": {"eps": rng.choice([1e-5, 1e-6])}, "layers": layers}
     if rng.random() < 0.75:
-        config["embedding"] = {"bigram": {"buckets": rng.choice([7, 53, 1021, 4099]), "mul_prev": rng.choice([1, 31, 127, 100003]),
-                                          "mul_cur": rng.choice([1, 17, 7, 99991])}}
+        config["embedding"] = {"bigram": {"buckets": rng.choice([7, 53, 1019, 4099]), "mul_prev": rng.choice([1, 31, 131, 100003]),
+                                          "mul_cur": rng.choice([1, 19, 7, 99991])}}
     return config
 
 
