@@ -214,26 +214,26 @@ LONG = {"architecture": "Fekotar", "vocab": 90, "width": 128, "logit_scale": 0.5
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_prompts_of_many_hundred_tokens(tmp_path, cuda_device, dtype):
     """Portions of more than 512 tokens (from where the products with many rows and the grouped products of a
-    routed layer run on the tensor cores' own kernels in bfloat16) beside short ones: a prompt of 700 tokens
-    whole, the same in portions of 530, 2 and 168, and a second one of 600 that comes in beside decoded
-    tokens of the first."""
+    routed layer run on the tensor cores' own kernels in bfloat16) and of more than 1024 (from where the
+    products per head stage all of K at once) beside short ones: a prompt of 1100 tokens whole, one of 700 in
+    portions of 530, 2 and 168, and a third of 600 that comes in beside decoded tokens of the first."""
     config = LONG if dtype == "float32" else without_choice(LONG)
     folder = write_model(tmp_path / "long", config, seed=77, dtype=DTYPES[dtype])
-    requests = {"a": random_tokens(90, 712, seed=1), "b": random_tokens(90, 712, seed=2), "c": random_tokens(90, 606, seed=3)}
+    requests = {"a": random_tokens(90, 1112, seed=1), "b": random_tokens(90, 712, seed=2), "c": random_tokens(90, 606, seed=3)}
     every = lambda lo, hi: list(range(0, hi - lo, 37)) + [hi - lo - 1]
-    steps = [{"step": 0, "entries": [{"id": "a", "tokens": requests["a"][:700], "want": every(0, 700)}], "end": []},
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": requests["a"][:1100], "want": every(0, 1100)}], "end": []},
              {"step": 1, "entries": [{"id": "b", "tokens": requests["b"][:530], "want": every(0, 530)}], "end": []},
              {"step": 2, "entries": [{"id": "b", "tokens": requests["b"][530:532], "want": [0, 1]},
-                                     {"id": "a", "tokens": requests["a"][700:701], "want": [0]}], "end": []},
-             {"step": 3, "entries": [{"id": "a", "tokens": requests["a"][701:702], "want": [0]},
+                                     {"id": "a", "tokens": requests["a"][1100:1101], "want": [0]}], "end": []},
+             {"step": 3, "entries": [{"id": "a", "tokens": requests["a"][1101:1102], "want": [0]},
                                      {"id": "c", "tokens": requests["c"][:600], "want": every(0, 600)},
                                      {"id": "b", "tokens": requests["b"][532:700], "want": every(532, 700)}], "end": []}]
     for i in range(6):
-        steps.append({"step": 4 + i, "entries": [{"id": "a", "tokens": [requests["a"][702 + i]], "want": [0]},
+        steps.append({"step": 4 + i, "entries": [{"id": "a", "tokens": [requests["a"][1102 + i]], "want": [0]},
                                                  {"id": "c", "tokens": [requests["c"][600 + i]], "want": [0]},
                                                  {"id": "b", "tokens": [requests["b"][700 + i]], "want": [0]}],
                       "end": ["a", "b", "c"] if i == 5 else []})
-    requests = {"a": requests["a"][:708], "b": requests["b"][:706], "c": requests["c"][:606]}
+    requests = {"a": requests["a"][:1108], "b": requests["b"][:706], "c": requests["c"][:606]}
     rows = collect(steps, replay(folder, dtype, steps, 32))
     assert len(rows) > 60
     assert_rows_match(rows, requests, folder, dtype, "long prompts")
@@ -485,7 +485,10 @@ def test_sigmoid_routing_limited_to_groups(cuda_device, experts, top, groups, sc
 @pytest.mark.parametrize("gate_kind", ["none", "head", "value"])
 @pytest.mark.parametrize("x_dtype,w_dtype", [("float32", "float32"), ("bfloat16", "bfloat16"), ("float32", "bfloat16")])
 @pytest.mark.parametrize("tokens,heads,n,k,x_head,y_head", [(1, 3, 48, 16, 24, 60), (70, 2, 20, 8, 8, 20), (200, 5, 130, 24, 29, 131),
-                                                            (33, 8, 16, 128, 160, 16)])
+                                                            (33, 8, 16, 128, 160, 16), (200, 5, 130, 160, 192, 131),
+                                                            (150, 3, 96, 512, 512, 128), (65, 2, 128, 32, 40, 128),
+                                                            (300, 4, 250, 48, 48, 250), (1030, 3, 96, 128, 160, 128),
+                                                            (1100, 2, 130, 48, 48, 131), (1024, 5, 250, 16, 24, 250)])
 def test_products_per_head_on_slices_of_wider_heads(cuda_device, x_dtype, w_dtype, tokens, heads, n, k, x_head, y_head, gate_kind):
     from zephyr_b200.kernels import ops
 
@@ -508,6 +511,13 @@ def test_products_per_head_on_slices_of_wider_heads(cuda_device, x_dtype, w_dtyp
     bound = 1e-5 if w_dtype == "float32" else 2.0 ** -7
     assert (got[:, :, :n] - expected).abs().max() < bound * max(1.0, float(expected.abs().max()))
     assert (got[:, :, n:] == 7.0).all()                       # what lies between the heads' outputs is left alone
+    if w_dtype == "bfloat16":
+        # 1024 rows and more, on 16-byte boundaries and with a K that is a multiple of 16, take the kernel that
+        # stages all of K at once: its sums are those of the walk along k, to the bit
+        walked = torch.full_like(out, 7.0)
+        ops.head_linear(x.to(cuda_device), w.to(cuda_device), gate=gate.to(cuda_device) if gate is not None else None,
+                        x_head_stride=x_head, out=walked, out_head_stride=y_head, walk=True)
+        assert torch.equal(out, walked)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -9,6 +9,13 @@
 // float32 sums in the order of k; W and y in the model's type (y may be float32), x in that type or in
 // float32 (a projection that was left unrounded).  float32 matrices run on CUDA cores, bfloat16 ones on
 // the tensor cores (x rounded to bfloat16 as it is staged).
+//
+// The op moves far more bytes than it multiplies (K and N are a head's sizes), so the bfloat16 form that
+// serves whole models stages ALL of K at once: a CTA asks for its 64 rows of x and up to 128 rows of the
+// head's matrix in one go (asynchronous 16-byte copies, or 16-byte loads that round float32 rows on
+// their way), waits once, multiplies out of shared memory and stores pairs of outputs.  Shapes whose rows
+// do not start on 16-byte boundaries, or whose K is no multiple of 16, and fewer than 1024 rows take the
+// tile walk in steps of 32.
 #include "tile_product.cuh"
 #include "tile_product_mma.cuh"
 
@@ -70,22 +77,190 @@ __global__ void __launch_bounds__(TM_THREADS) head_linear_mma_kernel(const HeadL
   const __nv_bfloat16* w = static_cast<const __nv_bfloat16*>(a.w) + (static_cast<size_t>(head) * a.N + n0) * a.K;
   float acc[2][4][4];
   tile_product_mma<false, X>(sm, w, nullptr, a.N - n0, a.K, a_vectors != 0, w_vectors != 0, acc);
+  // All gates first, then the stores: a load behind a store would wait for it.
+  float raw[4][4];
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const int t = t0 + tm_row(c);
+    const float* gate = a.gate != nullptr && t < a.tokens ? a.gate + t * a.gate_stride : nullptr;
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      const int n = n0 + tm_col(nt, c);
+      raw[c][nt] = 0.0f;
+      if (gate != nullptr && a.gate_per_element && n < a.N) raw[c][nt] = gate[static_cast<long long>(head) * a.N + n];
+      else if (gate != nullptr && !a.gate_per_element && nt == 0) raw[c][0] = gate[head];
+    }
+  }
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
     const int t = t0 + tm_row(c);
     if (t >= a.tokens) continue;
-    float mult = 1.0f;
-    const float* gate = a.gate != nullptr ? a.gate + t * a.gate_stride : nullptr;
-    if (gate != nullptr && !a.gate_per_element) mult = 1.0f / (1.0f + expf(-gate[head]));
     OUT* dst = static_cast<OUT*>(a.y) + t * a.y_stride + static_cast<long long>(head) * a.y_head_stride;
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt) {
       const int n = n0 + tm_col(nt, c);
       if (n >= a.N) continue;
-      if (gate != nullptr && a.gate_per_element) mult = 1.0f / (1.0f + expf(-gate[static_cast<long long>(head) * a.N + n]));
+      float mult = 1.0f;
+      if (a.gate != nullptr) mult = 1.0f / (1.0f + expf(-raw[c][a.gate_per_element ? nt : 0]));
       dst[n] = from_float<OUT>(acc[0][nt][c] * mult);
     }
   }
+}
+
+__device__ __forceinline__ void store_pair(float* p, float lo, float hi) { *reinterpret_cast<float2*>(p) = make_float2(lo, hi); }
+__device__ __forceinline__ void store_pair(__nv_bfloat16* p, float lo, float hi) {
+  *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(lo, hi);
+}
+
+constexpr int HW_BM = 64;        // rows of x a CTA
+constexpr int HW_BN = 128;       // outputs of the head a CTA
+constexpr int HW_THREADS = 256;
+constexpr int HW_MAX_K = 512;    // (64 + 128) rows of K + 8 bfloat16 values fit shared memory
+constexpr int HW_MIN_TOKENS = 1024;  // below, the walk's smaller tiles fill the SMs better (the sums are the same to the bit)
+
+// 8 warps: warp w owns rows 16 (w & 3) .. + 16 and outputs 64 (w >> 2) .. + 64, eight m16n8 tiles.
+// Rows of shared memory are K + 8 values apart, which spreads the fragment loads over all banks for
+// every K that is a multiple of 16.  `pairs` bit 0: every output row starts on an even element and on a
+// boundary of two elements' bytes, so two neighbouring outputs go out as one store; bit 1: the same for
+// the gates per output value, which then come in as pairs.
+template <typename X, typename OUT>
+__global__ void __launch_bounds__(HW_THREADS, 4) head_linear_whole_k_kernel(const HeadLinearArgs a, int pairs) {
+  extern __shared__ __align__(16) unsigned char hw_smem[];
+  const int K = a.K, ld = K + 8, pieces = K / 8;
+  __nv_bfloat16* sa = reinterpret_cast<__nv_bfloat16*>(hw_smem);      // [HW_BM][ld]
+  __nv_bfloat16* sb = sa + HW_BM * ld;                                 // [HW_BN][ld]
+  const int t0 = blockIdx.x * HW_BM, n0 = blockIdx.y * HW_BN, head = blockIdx.z, tid = threadIdx.x;
+  const int n_here = min(HW_BN, a.N - n0), rows_here = min(HW_BM, a.tokens - t0);
+  const int n_tiles = (n_here + 7) / 8 * 8;                            // rows of the matrix that are multiplied at all
+  const __nv_bfloat16* w = static_cast<const __nv_bfloat16*>(a.w) + (static_cast<size_t>(head) * a.N + n0) * K;
+  if (a.gate != nullptr && a.gate_per_element) {
+    // The gates are read last, when the sums are there: ask for their lines now, so that they wait in L2.
+    for (int e = tid; e < rows_here * ((n_here + 31) / 32); e += HW_THREADS) {
+      const int r = e / ((n_here + 31) / 32), line = e - r * ((n_here + 31) / 32);
+      const float* p = a.gate + (t0 + r) * a.gate_stride + static_cast<long long>(head) * a.N + n0 + min(line * 32, n_here - 1);
+      asm volatile("prefetch.L2 [%0];\n" ::"l"(p));
+    }
+  }
+  for (int e = tid; e < n_tiles * pieces; e += HW_THREADS) {
+    const int r = e / pieces, c = e - r * pieces;
+    cp_async_16(sb + r * ld + c * 8, w + static_cast<size_t>(r < n_here ? r : 0) * K + c * 8, r < n_here);
+  }
+  const X* x = static_cast<const X*>(a.x) + static_cast<long long>(t0) * a.x_stride + static_cast<long long>(head) * a.x_head_stride;
+  if (sizeof(X) == 2) {
+    for (int e = tid; e < HW_BM * pieces; e += HW_THREADS) {
+      const int r = e / pieces, c = e - r * pieces;
+      cp_async_16(sa + r * ld + c * 8, x + static_cast<long long>(r < rows_here ? r : 0) * a.x_stride + c * 8, r < rows_here);
+    }
+  } else {
+    // float32 rows: four pieces a thread are on their way before the first is rounded and stored.
+    for (int e0 = tid; e0 < HW_BM * pieces; e0 += 4 * HW_THREADS) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int e = e0 + u * HW_THREADS, r = e / pieces, c = e - r * pieces;
+        v[u] = e < HW_BM * pieces && r < rows_here ? tm_load8(x + static_cast<long long>(r) * a.x_stride + c * 8)
+                                                   : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int e = e0 + u * HW_THREADS, r = e / pieces, c = e - r * pieces;
+        if (e < HW_BM * pieces) *reinterpret_cast<uint4*>(sa + r * ld + c * 8) = v[u];
+      }
+    }
+  }
+  cp_async_commit();
+  cp_async_wait<0>();
+  __syncthreads();
+
+  const int warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int m0 = (warp & 3) * 16, nb = (warp >> 2) * 64;
+  float acc[8][4];
+#pragma unroll
+  for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) acc[nt][c] = 0.0f;
+  if (m0 < rows_here && nb < n_here) {
+    const __nv_bfloat16* a_lo = sa + (m0 + g) * ld + 2 * t;
+    const __nv_bfloat16* a_hi = a_lo + 8 * ld;
+    const __nv_bfloat16* b_row = sb + (nb + g) * ld + 2 * t;
+    for (int kk = 0; kk < K; kk += 16) {
+      unsigned af[4];
+      af[0] = *reinterpret_cast<const unsigned*>(a_lo + kk);
+      af[1] = *reinterpret_cast<const unsigned*>(a_hi + kk);
+      af[2] = *reinterpret_cast<const unsigned*>(a_lo + kk + 8);
+      af[3] = *reinterpret_cast<const unsigned*>(a_hi + kk + 8);
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        if (nb + nt * 8 >= n_here) break;                     // uniform over the warp
+        const __nv_bfloat16* b = b_row + nt * 8 * ld + kk;
+        mma_bf16_16816(acc[nt], af, *reinterpret_cast<const unsigned*>(b), *reinterpret_cast<const unsigned*>(b + 8));
+      }
+    }
+  }
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int row = t0 + m0 + g + 8 * half;
+    if (row >= a.tokens) continue;
+    const float* gate = a.gate != nullptr ? a.gate + row * a.gate_stride : nullptr;
+    // All of the row's gates first, then the stores: a load behind a store would wait for it.
+    float mult[8][2];
+    if (gate != nullptr && a.gate_per_element) {
+      float raw[8][2];
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        const int n = n0 + nb + nt * 8 + 2 * t;
+        const float* gv = gate + static_cast<long long>(head) * a.N + n;
+        raw[nt][0] = raw[nt][1] = 0.0f;
+        if ((pairs & 2) && n + 1 < a.N) {
+          const float2 two = *reinterpret_cast<const float2*>(gv);
+          raw[nt][0] = two.x;
+          raw[nt][1] = two.y;
+        } else {
+          if (n < a.N) raw[nt][0] = gv[0];
+          if (n + 1 < a.N) raw[nt][1] = gv[1];
+        }
+      }
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        mult[nt][0] = 1.0f / (1.0f + expf(-raw[nt][0]));
+        mult[nt][1] = 1.0f / (1.0f + expf(-raw[nt][1]));
+      }
+    } else {
+      const float head_mult = gate != nullptr ? 1.0f / (1.0f + expf(-gate[head])) : 1.0f;
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) mult[nt][0] = mult[nt][1] = head_mult;
+    }
+    OUT* dst = static_cast<OUT*>(a.y) + row * a.y_stride + static_cast<long long>(head) * a.y_head_stride;
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+      const int n = n0 + nb + nt * 8 + 2 * t;
+      if (n >= a.N) continue;
+      const float v0 = acc[nt][2 * half] * mult[nt][0], v1 = acc[nt][2 * half + 1] * mult[nt][1];
+      if ((pairs & 1) && n + 1 < a.N) {
+        store_pair(dst + n, v0, v1);
+      } else {
+        dst[n] = from_float<OUT>(v0);
+        if (n + 1 < a.N) dst[n + 1] = from_float<OUT>(v1);
+      }
+    }
+  }
+}
+
+template <typename X, typename OUT>
+int head_linear_whole_k_launch(const HeadLinearArgs& a, cudaStream_t s) {
+  const size_t smem = static_cast<size_t>(HW_BM + HW_BN) * (a.K + 8) * sizeof(__nv_bfloat16);
+  auto kernel = head_linear_whole_k_kernel<X, OUT>;
+  static size_t allowed = 48 * 1024;         // of this instantiation; raised once per larger K
+  if (smem > allowed) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
+      return ERR_CUDA;
+    allowed = smem;
+  }
+  const bool pairs = tm_aligned(a.y, 2 * sizeof(OUT)) && a.y_stride % 2 == 0 && a.y_head_stride % 2 == 0;
+  const bool gate_pairs = a.gate != nullptr && a.gate_per_element && tm_aligned(a.gate, 8) && a.gate_stride % 2 == 0 && a.N % 2 == 0;
+  const dim3 grid((a.tokens + HW_BM - 1) / HW_BM, (a.N + HW_BN - 1) / HW_BN, a.heads);
+  kernel<<<grid, HW_THREADS, smem, s>>>(a, (pairs ? 1 : 0) | (gate_pairs ? 2 : 0));
+  return launch_result();
 }
 
 }  // namespace zb
@@ -93,11 +268,12 @@ __global__ void __launch_bounds__(TM_THREADS) head_linear_mma_kernel(const HeadL
 using namespace zb;
 
 // The general form: head h reads K values from x[t, h * x_head_stride ...] and writes N values to
-// y[t, h * y_head_stride ...]; gate_per_element: one gate logit per output value instead of one per head.
+// y[t, h * y_head_stride ...]; gate_per_element: one gate logit per output value instead of one per head;
+// walk: take the tile walk in steps along k also where the shape allows all of K at once (for comparison).
 ZB_API int zb_head_linear_strided(void* y, const void* x, const void* w, const float* gate, long long x_stride,
                                   long long y_stride, long long gate_stride, int x_head_stride, int y_head_stride,
                                   int gate_per_element, int tokens, int heads, int N, int K, int x_dtype, int dtype,
-                                  int out_dtype, void* stream) {
+                                  int out_dtype, int walk, void* stream) {
   if (tokens < 0 || heads <= 0 || N <= 0 || K <= 0 || heads > 65535 || x_head_stride < K || y_head_stride < N)
     return ERR_BAD_ARGUMENT;
   if (tokens == 0) return OK;
@@ -115,6 +291,12 @@ ZB_API int zb_head_linear_strided(void* y, const void* x, const void* w, const f
   }
   const dim3 wide((tokens + TM_BM - 1) / TM_BM, (N + TM_BN - 1) / TM_BN, heads);
   const int w_vectors = K % 8 == 0 && tm_aligned(w, 16);
+  const int per16 = x_dtype == DTYPE_F32 ? 4 : 8;          // elements of x in 16 bytes
+  if (!walk && tokens >= HW_MIN_TOKENS && K % 16 == 0 && K <= HW_MAX_K && w_vectors && x_stride % per16 == 0 && x_head_stride % per16 == 0 && tm_aligned(x, 16)) {
+    if (x_dtype == DTYPE_F32)
+      return out_dtype == DTYPE_F32 ? head_linear_whole_k_launch<float, float>(a, s) : head_linear_whole_k_launch<float, bf16>(a, s);
+    return out_dtype == DTYPE_F32 ? head_linear_whole_k_launch<bf16, float>(a, s) : head_linear_whole_k_launch<bf16, bf16>(a, s);
+  }
   if (x_dtype == DTYPE_F32) {
     const int a_vectors = K % 8 == 0 && x_stride % 4 == 0 && x_head_stride % 4 == 0 && tm_aligned(x, 16);
     if (out_dtype == DTYPE_F32) head_linear_mma_kernel<float, float><<<wide, TM_THREADS, 0, s>>>(a, a_vectors, w_vectors);
@@ -131,5 +313,5 @@ ZB_API int zb_head_linear(void* y, const void* x, const void* w, const float* ga
                           long long y_stride, long long gate_stride, int tokens, int heads, int N, int K, int x_dtype,
                           int dtype, int out_dtype, void* stream) {
   return zb_head_linear_strided(y, x, w, gate, x_stride, y_stride, gate_stride, K, N, 0, tokens, heads, N, K, x_dtype,
-                                dtype, out_dtype, stream);
+                                dtype, out_dtype, 0, stream);
 }

@@ -566,16 +566,33 @@ def experts(args) -> dict:
 
 
 def head_linear(args) -> dict:
-    """The product per head: ``--tokens`` rows of ``--heads`` heads, [n, k] per head."""
+    """The product per head: ``--tokens`` rows of ``--heads`` heads, [n, k] per head; all of K staged at once
+    beside the walk along k in steps; bfloat16 rows, then bfloat16 rows with a float32 gate per output value,
+    then float32 rows that are slices of wider heads (queries on their way into a latent space)."""
     device, bf = torch.device("cuda"), torch.bfloat16
     T, heads, N, K = args.tokens, args.heads, args.n, args.k
     copies = _copies(T * heads * (N + K) * 2)
-    x = [torch.randn((T, heads * K), device=device, dtype=bf) for _ in range(copies)]
     w = torch.randn((heads, N, K), device=device, dtype=bf)
-    us = _time(lambda i: ops.head_linear(x[i % copies], w), args.warmup, args.iters)
-    flops, moved = 2.0 * T * heads * N * K, T * heads * (N + K) * 2 + heads * N * K * 2
-    return {"kernel": "head_linear_mma_kernel", "tokens": T, "heads": heads, "n": N, "k": K, "us": round(us, 2),
-            "tflops": round(flops / us / 1e6, 1), "gbs": round(moved / us / 1e3, 1)}
+    flops = 2.0 * T * heads * N * K
+    out = {"kernel": "head_linear_whole_k_kernel", "tokens": T, "heads": heads, "n": N, "k": K}
+
+    def both(name, moved, call):
+        for label, walk in (("", False), (", walk", True)):
+            us = _time(lambda i: call(i, walk), args.warmup, args.iters)
+            out[name + label] = {"us": round(us, 2), "tflops": round(flops / us / 1e6, 1), "gbs": round(moved / us / 1e3, 1)}
+
+    x = [torch.randn((T, heads * K), device=device, dtype=bf) for _ in range(copies)]
+    both("bf16 rows", T * heads * (N + K) * 2 + heads * N * K * 2, lambda i, walk: ops.head_linear(x[i % copies], w, walk=walk))
+    gates = [torch.randn((T, heads * N), device=device) for _ in range(copies)]
+    both("bf16 rows, a gate per value", T * heads * (N * 6 + K * 2) + heads * N * K * 2,
+         lambda i, walk: ops.head_linear(x[i % copies], w, gate=gates[i % copies], walk=walk))
+    del x, gates
+    wide = K + 32
+    xf = [torch.randn((T, heads * wide), device=device) for _ in range(copies)]
+    y = torch.empty((T, heads * (N + 32)), device=device, dtype=bf)
+    both("float32 rows, slices of wider heads", T * heads * (N * 2 + K * 4) + heads * N * K * 2,
+         lambda i, walk: ops.head_linear(xf[i % copies], w, x_head_stride=wide, out=y, out_head_stride=N + 32, walk=walk))
+    return out
 
 
 CASES.update({"experts": experts, "head_linear": head_linear, "stream_parts": stream_parts})
