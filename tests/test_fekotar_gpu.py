@@ -512,12 +512,13 @@ def test_products_per_head_on_slices_of_wider_heads(cuda_device, x_dtype, w_dtyp
     assert (got[:, :, :n] - expected).abs().max() < bound * max(1.0, float(expected.abs().max()))
     assert (got[:, :, n:] == 7.0).all()                       # what lies between the heads' outputs is left alone
     if w_dtype == "bfloat16":
-        # 1024 rows and more, on 16-byte boundaries and with a K that is a multiple of 16, take the kernel that
-        # stages all of K at once: its sums are those of the walk along k, to the bit
-        walked = torch.full_like(out, 7.0)
-        ops.head_linear(x.to(cuda_device), w.to(cuda_device), gate=gate.to(cuda_device) if gate is not None else None,
-                        x_head_stride=x_head, out=walked, out_head_stride=y_head, walk=True)
-        assert torch.equal(out, walked)
+        # rows on 16-byte boundaries with a K that is a multiple of 16 may take a kernel that stages all of K at
+        # once, with 32 or 64 rows a CTA by the row count: the sums are those of the walk along k, to the bit
+        for form in (1, 2, 3):
+            other = torch.full_like(out, 7.0)
+            ops.head_linear(x.to(cuda_device), w.to(cuda_device), gate=gate.to(cuda_device) if gate is not None else None,
+                            x_head_stride=x_head, out=other, out_head_stride=y_head, walk=form)
+            assert torch.equal(out, other), form
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

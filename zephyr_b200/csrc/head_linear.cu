@@ -14,8 +14,8 @@
 // serves whole models stages ALL of K at once: a CTA asks for its 64 rows of x and up to 128 rows of the
 // head's matrix in one go (asynchronous 16-byte copies, or 16-byte loads that round float32 rows on
 // their way), waits once, multiplies out of shared memory and stores pairs of outputs.  Shapes whose rows
-// do not start on 16-byte boundaries, or whose K is no multiple of 16, and fewer than 1024 rows take the
-// tile walk in steps of 32.
+// do not start on 16-byte boundaries, or whose K is no multiple of 16, and fewer than a few hundred rows take
+// the tile walk in steps of 32.
 #include "tile_product.cuh"
 #include "tile_product_mma.cuh"
 
@@ -112,25 +112,29 @@ __device__ __forceinline__ void store_pair(__nv_bfloat16* p, float lo, float hi)
   *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(lo, hi);
 }
 
-constexpr int HW_BM = 64;        // rows of x a CTA
 constexpr int HW_BN = 128;       // outputs of the head a CTA
 constexpr int HW_THREADS = 256;
 constexpr int HW_MAX_K = 512;    // (64 + 128) rows of K + 8 bfloat16 values fit shared memory
-constexpr int HW_MIN_TOKENS = 1024;  // below, the walk's smaller tiles fill the SMs better (the sums are the same to the bit)
+// Which form runs (the sums are the same to the bit): 64 rows a CTA from HW_ROWS_64 rows on, 32 rows a CTA from
+// HW_ROWS_32 on (more and smaller CTAs while there are few), below that the walk, whose still smaller tiles
+// fill the SMs better.  Measured at 16 heads of 128 x 128.
+constexpr int HW_ROWS_64 = 1536;
+constexpr int HW_ROWS_32 = 384;
 
-// 8 warps: warp w owns rows 16 (w & 3) .. + 16 and outputs 64 (w >> 2) .. + 64, eight m16n8 tiles.
+// BM rows of x a CTA (64, or 32 for more and smaller CTAs).  8 warps: BM / 16 of them along the rows, the others
+// along the outputs, each with 16 rows and 128 / (8 / (BM / 16)) outputs: eight or four m16n8 tiles.
 // Rows of shared memory are K + 8 values apart, which spreads the fragment loads over all banks for
 // every K that is a multiple of 16.  `pairs` bit 0: every output row starts on an even element and on a
 // boundary of two elements' bytes, so two neighbouring outputs go out as one store; bit 1: the same for
 // the gates per output value, which then come in as pairs.
-template <typename X, typename OUT>
-__global__ void __launch_bounds__(HW_THREADS, 4) head_linear_whole_k_kernel(const HeadLinearArgs a, int pairs) {
+template <typename X, typename OUT, int BM>
+__global__ void __launch_bounds__(HW_THREADS, BM == 32 ? 5 : 4) head_linear_whole_k_kernel(const HeadLinearArgs a, int pairs) {
   extern __shared__ __align__(16) unsigned char hw_smem[];
   const int K = a.K, ld = K + 8, pieces = K / 8;
-  __nv_bfloat16* sa = reinterpret_cast<__nv_bfloat16*>(hw_smem);      // [HW_BM][ld]
-  __nv_bfloat16* sb = sa + HW_BM * ld;                                 // [HW_BN][ld]
-  const int t0 = blockIdx.x * HW_BM, n0 = blockIdx.y * HW_BN, head = blockIdx.z, tid = threadIdx.x;
-  const int n_here = min(HW_BN, a.N - n0), rows_here = min(HW_BM, a.tokens - t0);
+  __nv_bfloat16* sa = reinterpret_cast<__nv_bfloat16*>(hw_smem);      // [BM][ld]
+  __nv_bfloat16* sb = sa + BM * ld;                                 // [HW_BN][ld]
+  const int t0 = blockIdx.x * BM, n0 = blockIdx.y * HW_BN, head = blockIdx.z, tid = threadIdx.x;
+  const int n_here = min(HW_BN, a.N - n0), rows_here = min(BM, a.tokens - t0);
   const int n_tiles = (n_here + 7) / 8 * 8;                            // rows of the matrix that are multiplied at all
   const __nv_bfloat16* w = static_cast<const __nv_bfloat16*>(a.w) + (static_cast<size_t>(head) * a.N + n0) * K;
   if (a.gate != nullptr && a.gate_per_element) {
@@ -147,24 +151,24 @@ __global__ void __launch_bounds__(HW_THREADS, 4) head_linear_whole_k_kernel(cons
   }
   const X* x = static_cast<const X*>(a.x) + static_cast<long long>(t0) * a.x_stride + static_cast<long long>(head) * a.x_head_stride;
   if (sizeof(X) == 2) {
-    for (int e = tid; e < HW_BM * pieces; e += HW_THREADS) {
+    for (int e = tid; e < BM * pieces; e += HW_THREADS) {
       const int r = e / pieces, c = e - r * pieces;
       cp_async_16(sa + r * ld + c * 8, x + static_cast<long long>(r < rows_here ? r : 0) * a.x_stride + c * 8, r < rows_here);
     }
   } else {
     // float32 rows: four pieces a thread are on their way before the first is rounded and stored.
-    for (int e0 = tid; e0 < HW_BM * pieces; e0 += 4 * HW_THREADS) {
+    for (int e0 = tid; e0 < BM * pieces; e0 += 4 * HW_THREADS) {
       uint4 v[4];
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         const int e = e0 + u * HW_THREADS, r = e / pieces, c = e - r * pieces;
-        v[u] = e < HW_BM * pieces && r < rows_here ? tm_load8(x + static_cast<long long>(r) * a.x_stride + c * 8)
+        v[u] = e < BM * pieces && r < rows_here ? tm_load8(x + static_cast<long long>(r) * a.x_stride + c * 8)
                                                    : make_uint4(0, 0, 0, 0);
       }
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         const int e = e0 + u * HW_THREADS, r = e / pieces, c = e - r * pieces;
-        if (e < HW_BM * pieces) *reinterpret_cast<uint4*>(sa + r * ld + c * 8) = v[u];
+        if (e < BM * pieces) *reinterpret_cast<uint4*>(sa + r * ld + c * 8) = v[u];
       }
     }
   }
@@ -173,10 +177,11 @@ __global__ void __launch_bounds__(HW_THREADS, 4) head_linear_whole_k_kernel(cons
   __syncthreads();
 
   const int warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-  const int m0 = (warp & 3) * 16, nb = (warp >> 2) * 64;
-  float acc[8][4];
+  constexpr int MW = BM / 16, NT = HW_BN / (8 / MW) / 8;     // warps along the rows; m16n8 tiles a warp
+  const int m0 = (warp % MW) * 16, nb = (warp / MW) * (NT * 8);
+  float acc[NT][4];
 #pragma unroll
-  for (int nt = 0; nt < 8; ++nt)
+  for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
     for (int c = 0; c < 4; ++c) acc[nt][c] = 0.0f;
   if (m0 < rows_here && nb < n_here) {
@@ -190,7 +195,7 @@ __global__ void __launch_bounds__(HW_THREADS, 4) head_linear_whole_k_kernel(cons
       af[2] = *reinterpret_cast<const unsigned*>(a_lo + kk + 8);
       af[3] = *reinterpret_cast<const unsigned*>(a_hi + kk + 8);
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
+      for (int nt = 0; nt < NT; ++nt) {
         if (nb + nt * 8 >= n_here) break;                     // uniform over the warp
         const __nv_bfloat16* b = b_row + nt * 8 * ld + kk;
         mma_bf16_16816(acc[nt], af, *reinterpret_cast<const unsigned*>(b), *reinterpret_cast<const unsigned*>(b + 8));
@@ -203,11 +208,11 @@ __global__ void __launch_bounds__(HW_THREADS, 4) head_linear_whole_k_kernel(cons
     if (row >= a.tokens) continue;
     const float* gate = a.gate != nullptr ? a.gate + row * a.gate_stride : nullptr;
     // All of the row's gates first, then the stores: a load behind a store would wait for it.
-    float mult[8][2];
+    float mult[NT][2];
     if (gate != nullptr && a.gate_per_element) {
-      float raw[8][2];
+      float raw[NT][2];
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
+      for (int nt = 0; nt < NT; ++nt) {
         const int n = n0 + nb + nt * 8 + 2 * t;
         const float* gv = gate + static_cast<long long>(head) * a.N + n;
         raw[nt][0] = raw[nt][1] = 0.0f;
@@ -221,18 +226,18 @@ __global__ void __launch_bounds__(HW_THREADS, 4) head_linear_whole_k_kernel(cons
         }
       }
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
+      for (int nt = 0; nt < NT; ++nt) {
         mult[nt][0] = 1.0f / (1.0f + expf(-raw[nt][0]));
         mult[nt][1] = 1.0f / (1.0f + expf(-raw[nt][1]));
       }
     } else {
       const float head_mult = gate != nullptr ? 1.0f / (1.0f + expf(-gate[head])) : 1.0f;
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt) mult[nt][0] = mult[nt][1] = head_mult;
+      for (int nt = 0; nt < NT; ++nt) mult[nt][0] = mult[nt][1] = head_mult;
     }
     OUT* dst = static_cast<OUT*>(a.y) + row * a.y_stride + static_cast<long long>(head) * a.y_head_stride;
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt) {
+    for (int nt = 0; nt < NT; ++nt) {
       const int n = n0 + nb + nt * 8 + 2 * t;
       if (n >= a.N) continue;
       const float v0 = acc[nt][2 * half] * mult[nt][0], v1 = acc[nt][2 * half + 1] * mult[nt][1];
@@ -246,10 +251,10 @@ __global__ void __launch_bounds__(HW_THREADS, 4) head_linear_whole_k_kernel(cons
   }
 }
 
-template <typename X, typename OUT>
+template <typename X, typename OUT, int BM>
 int head_linear_whole_k_launch(const HeadLinearArgs& a, cudaStream_t s) {
-  const size_t smem = static_cast<size_t>(HW_BM + HW_BN) * (a.K + 8) * sizeof(__nv_bfloat16);
-  auto kernel = head_linear_whole_k_kernel<X, OUT>;
+  const size_t smem = static_cast<size_t>(BM + HW_BN) * (a.K + 8) * sizeof(__nv_bfloat16);
+  auto kernel = head_linear_whole_k_kernel<X, OUT, BM>;
   static size_t allowed = 48 * 1024;         // of this instantiation; raised once per larger K
   if (smem > allowed) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
@@ -258,7 +263,7 @@ int head_linear_whole_k_launch(const HeadLinearArgs& a, cudaStream_t s) {
   }
   const bool pairs = tm_aligned(a.y, 2 * sizeof(OUT)) && a.y_stride % 2 == 0 && a.y_head_stride % 2 == 0;
   const bool gate_pairs = a.gate != nullptr && a.gate_per_element && tm_aligned(a.gate, 8) && a.gate_stride % 2 == 0 && a.N % 2 == 0;
-  const dim3 grid((a.tokens + HW_BM - 1) / HW_BM, (a.N + HW_BN - 1) / HW_BN, a.heads);
+  const dim3 grid((a.tokens + BM - 1) / BM, (a.N + HW_BN - 1) / HW_BN, a.heads);
   kernel<<<grid, HW_THREADS, smem, s>>>(a, (pairs ? 1 : 0) | (gate_pairs ? 2 : 0));
   return launch_result();
 }
@@ -269,7 +274,8 @@ using namespace zb;
 
 // The general form: head h reads K values from x[t, h * x_head_stride ...] and writes N values to
 // y[t, h * y_head_stride ...]; gate_per_element: one gate logit per output value instead of one per head;
-// walk: take the tile walk in steps along k also where the shape allows all of K at once (for comparison).
+// walk: 0 the form that suits the shape and the row count; for comparison, where the shape allows all of K at
+// once: 1 the tile walk in steps along k, 2 all of K with 32 rows a CTA, 3 with 64.
 ZB_API int zb_head_linear_strided(void* y, const void* x, const void* w, const float* gate, long long x_stride,
                                   long long y_stride, long long gate_stride, int x_head_stride, int y_head_stride,
                                   int gate_per_element, int tokens, int heads, int N, int K, int x_dtype, int dtype,
@@ -292,10 +298,17 @@ ZB_API int zb_head_linear_strided(void* y, const void* x, const void* w, const f
   const dim3 wide((tokens + TM_BM - 1) / TM_BM, (N + TM_BN - 1) / TM_BN, heads);
   const int w_vectors = K % 8 == 0 && tm_aligned(w, 16);
   const int per16 = x_dtype == DTYPE_F32 ? 4 : 8;          // elements of x in 16 bytes
-  if (!walk && tokens >= HW_MIN_TOKENS && K % 16 == 0 && K <= HW_MAX_K && w_vectors && x_stride % per16 == 0 && x_head_stride % per16 == 0 && tm_aligned(x, 16)) {
+  const bool all_of_k = K % 16 == 0 && K <= HW_MAX_K && w_vectors && x_stride % per16 == 0 && x_head_stride % per16 == 0 &&
+                        tm_aligned(x, 16);
+  if (all_of_k && walk != 1 && (walk >= 2 || tokens >= HW_ROWS_32)) {
+    if (walk == 2 || (walk == 0 && tokens < HW_ROWS_64)) {
+      if (x_dtype == DTYPE_F32)
+        return out_dtype == DTYPE_F32 ? head_linear_whole_k_launch<float, float, 32>(a, s) : head_linear_whole_k_launch<float, bf16, 32>(a, s);
+      return out_dtype == DTYPE_F32 ? head_linear_whole_k_launch<bf16, float, 32>(a, s) : head_linear_whole_k_launch<bf16, bf16, 32>(a, s);
+    }
     if (x_dtype == DTYPE_F32)
-      return out_dtype == DTYPE_F32 ? head_linear_whole_k_launch<float, float>(a, s) : head_linear_whole_k_launch<float, bf16>(a, s);
-    return out_dtype == DTYPE_F32 ? head_linear_whole_k_launch<bf16, float>(a, s) : head_linear_whole_k_launch<bf16, bf16>(a, s);
+      return out_dtype == DTYPE_F32 ? head_linear_whole_k_launch<float, float, 64>(a, s) : head_linear_whole_k_launch<float, bf16, 64>(a, s);
+    return out_dtype == DTYPE_F32 ? head_linear_whole_k_launch<bf16, float, 64>(a, s) : head_linear_whole_k_launch<bf16, bf16, 64>(a, s);
   }
   if (x_dtype == DTYPE_F32) {
     const int a_vectors = K % 8 == 0 && x_stride % 4 == 0 && x_head_stride % 4 == 0 && tm_aligned(x, 16);

@@ -1404,7 +1404,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = Non
 # ------------------------------------------------------------- products per head and per expert
 def head_linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None,
                 gate: torch.Tensor | None = None, x_head_stride: int | None = None,
-                out: torch.Tensor | None = None, out_head_stride: int | None = None, walk: bool = False) -> torch.Tensor:
+                out: torch.Tensor | None = None, out_head_stride: int | None = None, walk: int = 0) -> torch.Tensor:
     """y[t, h, :] = w[h] x[t, h, :] for x [T, heads * K] (unit inner stride) and w [heads, N, K]: a product
     that is block-diagonal over heads; returns [T, heads * N] in ``out_dtype`` (default: w's type).  x may be
     float32 beside bfloat16 matrices.  ``gate`` (float32, unit inner stride): [T, >= heads] multiplies head
@@ -1414,9 +1414,9 @@ def head_linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None 
     ``x_head_stride``: head h's K inputs start at x[t, h * x_head_stride] (heads that are slices of wider
     ones; x is then [T, >= heads * x_head_stride]).  ``out`` with ``out_head_stride``: head h's N outputs go
     to out[t, h * out_head_stride ...] of a given [T, heads * out_head_stride] tensor, the rest of which is
-    left as it is.  ``walk``: the bfloat16 kernel that walks along k in steps, also where rows start on 16-byte
-    boundaries and K is a multiple of 16, which otherwise take the kernel that stages all of K at once (the
-    sums are the same to the bit)."""
+    left as it is.  ``walk``: which bfloat16 kernel runs where rows start on 16-byte boundaries and K is a
+    multiple of 16: 0 by the row count, 1 the walk along k in steps, 2 and 3 all of K at once with 32 and 64
+    rows a CTA (the sums are the same to the bit)."""
     _cuda(x, w, gate, out)
     heads, N, K = w.shape
     xhs = K if x_head_stride is None else int(x_head_stride)

@@ -577,7 +577,7 @@ def head_linear(args) -> dict:
     out = {"kernel": "head_linear_whole_k_kernel", "tokens": T, "heads": heads, "n": N, "k": K}
 
     def both(name, moved, call):
-        for label, walk in (("", False), (", walk", True)):
+        for label, walk in (("", 0), (", walk", 1), (", 32 rows a CTA", 2), (", 64 rows a CTA", 3)):
             us = _time(lambda i: call(i, walk), args.warmup, args.iters)
             out[name + label] = {"us": round(us, 2), "tflops": round(flops / us / 1e6, 1), "gbs": round(moved / us / 1e3, 1)}
 
