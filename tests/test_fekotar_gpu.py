@@ -525,7 +525,9 @@ def test_products_per_head_on_slices_of_wider_heads(cuda_device, x_dtype, w_dtyp
 @pytest.mark.parametrize("rank,rot,heads,page,scaling", [(40, 8, 3, 16, yarn(4.0, 64, 8.0, 2.0)), (96, 32, 8, 16, yarn(8.0, 128, 16.0, 1.0)),
                                                          (28, 4, 6, 16, None), (64, 64, 16, 32, yarn(2.0, 16, 2.0, 0.25)),
                                                          (128, 32, 4, 32, None), (30, 2, 1, 16, None), (48, 16, 20, 16, yarn(3.0, 50, 5.0, 1.0)),
-                                                         (512, 64, 2, 16, yarn(4.0, 64, 8.0, 1.0)), (700, 68, 1, 32, None)])
+                                                         (512, 64, 2, 16, yarn(4.0, 64, 8.0, 1.0)), (700, 68, 1, 32, None),
+                                                         (160, 32, 18, 16, None), (200, 24, 3, 32, yarn(2.0, 64, 8.0, 1.0)),
+                                                         (192, 64, 5, 16, None)])
 def test_attention_over_a_latent_with_a_rotated_part(cuda_device, dtype, rank, rot, heads, page, scaling):
     """The cached row is the normed latent followed by the rotated key part; queries carry the same two
     pieces.  Queries of head 0 point at one row each THROUGH THE ROTATED PART ONLY (the latent part of those
@@ -568,6 +570,7 @@ def test_attention_over_a_latent_with_a_rotated_part(cuda_device, dtype, rank, r
     status = ops.new_status(cuda_device)
     tile = ops.attention_tile_tokens(heads)
     fast_ok = ops.paged_decode_supported(heads, 1, width, torch_dtype)
+    prompt_ok = ops.paged_prefill_supported(heads, 1, width, torch_dtype)     # single tokens too, as tiles of one token
     outs, fast_outs, at = [], [], 0
     for n in [T - 12] + [1] * 12:
         rows = _rows(n, at, cuda_device)
@@ -580,9 +583,9 @@ def test_attention_over_a_latent_with_a_rotated_part(cuda_device, dtype, rank, r
         tile_q0 = torch.arange(0, n, tile, dtype=torch.int32, device=cuda_device)
         outs.append(ops.paged_attention(qs, cache, table, torch.zeros_like(tile_q0), tile_q0, tile, *rows, heads, 1, width, 0,
                                         scale, status, shared_kv=True))
-        if fast_ok:
+        if prompt_ok:
             fast = torch.full_like(outs[-1], float("nan"))
-            if n == 1:
+            if n == 1 and fast_ok:
                 ops.paged_decode(qs, cache, table, rows[0], rows[0], rows[2], at + 1, heads, 1, width, 0, scale, status, fast,
                                  keys_only=True)
             else:
@@ -594,11 +597,12 @@ def test_attention_over_a_latent_with_a_rotated_part(cuda_device, dtype, rank, r
         at += n
     ops.check_status(status)
     bound = (3e-5 if dtype == "float32" else 0.04) * max(1.0, float(expected.abs().max()))
-    for got in [torch.cat(outs)] + ([torch.cat(fast_outs)] if fast_ok else []):
+    for got in [torch.cat(outs)] + ([torch.cat(fast_outs)] if prompt_ok else []):
         got = got.cpu().double()
         assert torch.isfinite(got).all()
         assert (got - expected).abs().max() < bound
     assert fast_ok == (dtype == "bfloat16" and width in (32, 64, 96, 128) and heads <= 16)
+    assert prompt_ok == (dtype == "bfloat16" and width % 32 == 0 and width <= 256)
     if dtype == "float32" and rot >= 32:      # (fewer rotated values: other rows lie as close by chance)
         for p, target in targets.items():       # the pointed-at row decides head 0's output
             if target >= 0:

@@ -44,7 +44,7 @@ struct PrefillArgs {
 template <int HD>
 __global__ void __launch_bounds__(PRE_WARPS * 32, 1)
 paged_prefill_kernel(const PrefillArgs a) {
-  static_assert(HD % 32 == 0 && HD <= 128, "head sizes 32, 64, 96, 128");
+  static_assert(HD % 32 == 0 && HD <= 256, "head sizes that are multiples of 32, up to 256");
   constexpr int KROW = HD + 8;                      // padded rows: conflict-free ldmatrix
   constexpr int CHUNKS = HD / 8;
   constexpr int STAGE = 2 * PRE_BN * KROW;
@@ -248,7 +248,7 @@ ZB_API int zb_paged_prefill_tile_tokens() { return PRE_BM; }
 
 ZB_API int zb_paged_prefill_supported(int nh, int nkv, int hd, int dtype) {
   if (dtype != DTYPE_BF16 || nkv <= 0 || nh <= 0 || nh % nkv != 0 || nh > 65535) return 0;
-  return hd == 32 || hd == 64 || hd == 96 || hd == 128 ? 1 : 0;
+  return hd % 32 == 0 && hd >= 32 && hd <= 256 ? 1 : 0;
 }
 
 // Attention of the tiles' tokens over their requests' pages; writes those tokens' rows of `out`.
@@ -280,7 +280,11 @@ ZB_API int zb_paged_prefill_masked(void* out, const void* q, const void* kv_cach
     case 32: return prefill_launch<32>(a, n_tiles, s);
     case 64: return prefill_launch<64>(a, n_tiles, s);
     case 96: return prefill_launch<96>(a, n_tiles, s);
-    default: return prefill_launch<128>(a, n_tiles, s);
+    case 128: return prefill_launch<128>(a, n_tiles, s);
+    case 160: return prefill_launch<160>(a, n_tiles, s);
+    case 192: return prefill_launch<192>(a, n_tiles, s);
+    case 224: return prefill_launch<224>(a, n_tiles, s);
+    default: return prefill_launch<256>(a, n_tiles, s);
   }
 }
 

@@ -125,7 +125,8 @@ class LatentAttention(Mixer):
     @staticmethod
     def tile_requests(spec: MixerSpec) -> list[tuple[int, str]]:
         tokens = ops.attention_tile_tokens(int(spec.params["num_heads"]))
-        return [(tokens, "all"), (tokens, "multi"), (tokens, "single"), (ops.paged_prefill_tile_tokens(), "multi")]
+        wide = ops.paged_prefill_tile_tokens()
+        return [(tokens, "all"), (tokens, "multi"), (tokens, "single"), (wide, "multi"), (wide, "all")]
 
     def forward(self, x: torch.Tensor, ctx: StepContext, call: LayerCall,
                 out_dtype: torch.dtype | None = None) -> torch.Tensor:
@@ -161,8 +162,9 @@ class LatentAttention(Mixer):
 
     def attend(self, q: torch.Tensor, ctx: StepContext, cache: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
         """Attention of the latent-space queries [T, heads * (rank + rot)] over the cached rows: rows with one
-        new token on the split-context kernel, rows with several on the tensor-core prompt kernel, where
-        those take this shape and type; whatever is left on the general kernel."""
+        new token on the split-context kernel, rows with several on a tensor-core prompt kernel, where
+        those take this shape and type (the prompt kernels take more widths than the split-context one, and
+        then serve single tokens as well); whatever is left on the general kernel."""
         out = torch.empty_like(q)
         common = (self.nh, 1, self.kw, 0, self.scale, ctx.status)
         decode_done = self.fast_decode and ctx.num_decode_rows > 0
@@ -170,6 +172,15 @@ class LatentAttention(Mixer):
             ops.paged_decode(q, cache, table, ctx.decode_rows, ctx.row_q_start, ctx.row_ctx, ctx.max_decode_context,
                              *common, out=out, sinks=self.sinks, keys_only=True)
         prefill_done = False
+        if self.fast_prefill and not self.fast_decode:
+            # A row that the split-context kernel does not take (its width, or more than 16 heads): single tokens
+            # go through the tensor-core prompt kernel too, as tiles of one token; two orders of magnitude
+            # above the general kernel at contexts of thousands.
+            tile_row, tile_q0 = ctx.tiles[(self.prefill_tile_tokens, "all")]
+            if tile_row.numel() > 0:
+                ops.paged_prefill(q, cache, table, tile_row, tile_q0, ctx.row_q_start, ctx.row_q_len, ctx.row_ctx,
+                                  *common, out=out, sinks=self.sinks, keys_only=True)
+            return out
         if self.fast_prefill:
             tile_row, tile_q0 = ctx.tiles[(self.prefill_tile_tokens, "multi")]
             prefill_done = True
