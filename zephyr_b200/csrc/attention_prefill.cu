@@ -11,6 +11,11 @@
 // float32 accumulators; the softmax is online, in float32, in base 2 with scale*log2(e) folded
 // in; probabilities are rounded to bfloat16 for the second product.  Math and masking as in
 // attention_simt.cu (causal, lower-right aligned on the cached context, optional window).
+//
+// Head sizes: every multiple of 32 up to 256 (a query tile's outputs stay in registers: 16 float32
+// values a thread for every 32 of the head).  A tile may hold a single token (one warp works, the
+// others help to fetch): latent attention serves decoded tokens this way where the split-context
+// kernel does not take the cached row's width.
 #include "common.cuh"
 #include "mma.cuh"
 
