@@ -60,8 +60,8 @@ GEFOVIK_SIZES = {
 # ``--arch fekotar``: the same for the design whose layers run latent attention (queries through a latent of
 # their own, a rotated part, a gate per value) and a feed-forward side by side on one norm's output;
 # feed-forwards bounded dense and routed (16 experts in 4 groups of which 2 are kept, a token takes 4) in
-# turn.  A position keeps kv_rank + rot_dim = 128 values.  Beside it runs Gefovik, the closest design the
-# engine has, with latent attention over a latent of 128 in every layer and the same feed-forward sizes.
+# turn.  A position keeps kv_rank + rot_dim = 128 values (160 in the last entry).  Beside it runs Gefovik, the closest
+# design the engine has, with latent attention over a latent as wide in every layer and the same feed-forward sizes.
 FEKOTAR_SIZES = {
     "w1024": dict(width=1024, ff=3072, layers=8, heads=8, dim=128, rot_dim=32, vdim=128, kv_rank=96, q_rank=384, experts=16, top=4,
                   groups=(4, 2)),
@@ -69,6 +69,9 @@ FEKOTAR_SIZES = {
                   groups=(4, 2)),
     "w4096": dict(width=4096, ff=12288, layers=8, heads=16, dim=128, rot_dim=32, vdim=128, kv_rank=96, q_rank=1536, experts=16, top=4,
                   groups=(4, 2)),
+    # a position keeps 128 + 32 = 160 values: prompts and decoded tokens on the mma.sync prompt kernel
+    "w2048r160": dict(width=2048, ff=6144, layers=8, heads=16, dim=128, rot_dim=32, vdim=128, kv_rank=128, q_rank=768, experts=16,
+                      top=4, groups=(4, 2)),
 }
 
 
