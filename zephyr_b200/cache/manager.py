@@ -31,7 +31,11 @@ class PagedCacheSpec:
     value of ``value_dim`` values (the reference keeps the two widths apart per layer,
     src/include/kv_cache/cache_engine.hpp:18-22).  ``value_dim`` 0 means "as wide as the key".
     ``keys_only``: nothing is stored for the values; the reader takes the keys for them (a latent that is
-    key and value at once), and a page is half as large."""
+    key and value at once), and a page is half as large.
+    ``keep_first``: a windowed cache whose first n positions stay readable for good (the window passes
+    them, their pages are never given back).
+    ``every``: n > 1: the store holds one entry per run of n positions (entry b stands for positions
+    b n .. b n + n - 1: a mean of a block, say), so its tables cover ceil(positions / n) entries."""
 
     num_kv_heads: int
     key_dim: int
@@ -39,6 +43,8 @@ class PagedCacheSpec:
     window: int = 0        # 0: every position is kept; n: only the last n positions are ever read
     chunk: int = 0         # n > 0: a query at position p reads only positions >= (p // n) * n
     keys_only: bool = False
+    keep_first: int = 0
+    every: int = 1
 
     def __post_init__(self) -> None:
         if self.value_dim == 0:
@@ -54,7 +60,8 @@ class PagedCacheSpec:
 
     @property
     def group_key(self) -> tuple:
-        return ("paged", self.num_kv_heads, self.key_dim, self.value_dim, self.window, self.chunk, self.keys_only)
+        return ("paged", self.num_kv_heads, self.key_dim, self.value_dim, self.window, self.chunk, self.keys_only,
+                self.keep_first if self.window > 0 else 0, self.every)
 
     @property
     def stored_per_position(self) -> int:
@@ -145,6 +152,8 @@ class GroupState:
     cache_ids: list[int]
     pool: PagePool
     chunk: int = 0
+    keep_first: int = 0        # positions at the start that a window never lets go
+    every: int = 1             # positions per entry
 
 
 @dataclass
@@ -180,11 +189,17 @@ class CacheManager:
         by_key: dict[tuple, int] = {}
         for cache_id, spec in enumerate(self.cache_specs):
             if isinstance(spec, PagedCacheSpec):
-                if spec.window < 0 or spec.chunk < 0:
-                    raise InvalidArgumentError("a window or chunk cannot be negative")
+                if spec.window < 0 or spec.chunk < 0 or spec.keep_first < 0 or spec.every < 1:
+                    raise InvalidArgumentError("a window, chunk or kept start cannot be negative, and an entry stands for one position or more")
+                if spec.every > 1 and (spec.window > 0 or spec.chunk > 0):
+                    raise InvalidArgumentError("a store with one entry per run of positions keeps all its entries")
                 if spec.group_key not in by_key:
                     by_key[spec.group_key] = len(self.groups)
-                    self.groups.append(GroupState(spec.group_key, spec.window, [], PagePool(num_pages), spec.chunk))
+                    # A store of one entry per run of n positions needs 1/n of the pages, and one more
+                    # per request for each request's last, partly filled page.
+                    pages = num_pages if spec.every == 1 else min(num_pages, 2 + (num_pages - 2) // spec.every + max_requests)
+                    self.groups.append(GroupState(spec.group_key, spec.window, [], PagePool(pages), spec.chunk,
+                                                  spec.keep_first if spec.window > 0 else 0, spec.every))
                 index = by_key[spec.group_key]
                 self.groups[index].cache_ids.append(cache_id)
                 self.group_of_cache[cache_id] = index
@@ -203,14 +218,19 @@ class CacheManager:
     def blocks_for(self, tokens: int) -> int:
         return -(-tokens // self.page_size)
 
+    def group_blocks_for(self, group: GroupState, tokens: int) -> int:
+        """Pages of ``group`` that ``tokens`` positions take: a group with one entry per run of n positions
+        counts entries."""
+        return self.blocks_for(-(-tokens // group.every))
+
     def _live_blocks_needed(self, group: GroupState, length: int, step_tokens: int) -> int:
         """Pages a request of ``length`` positions holds at most at one time in ``group``, when no step
         brings more than ``step_tokens`` new positions."""
-        full = self.blocks_for(length)
+        full = self.group_blocks_for(group, length)
         reach = min([n for n in (group.window, group.chunk) if n > 0], default=0)
         if reach == 0:
             return full
-        return min(full, self.blocks_for(reach + step_tokens) + 1)
+        return min(full, self.blocks_for(reach + step_tokens) + 1 + self.blocks_for(group.keep_first))
 
     def num_free_pages(self, group: int = 0) -> int:
         return self.groups[group].pool.num_free
@@ -269,7 +289,7 @@ class CacheManager:
             return True
         needs = []
         for index, group in enumerate(self.groups):
-            extra = self.blocks_for(length) - len(request.tables[index])
+            extra = self.group_blocks_for(group, length) - len(request.tables[index])
             # Pages promised to other requests are not this request's to take; its own promise is.
             others_reserved = sum(r.reserved[index] for r in self._requests.values()) - request.reserved[index]
             if extra > group.pool.num_free - others_reserved:
@@ -308,13 +328,16 @@ class CacheManager:
             if group.chunk > 0:
                 dead = max(dead, (request.computed // group.chunk) * group.chunk // self.page_size)
             dead = min(dead, len(request.tables[index]))
-            if dead > request.released_blocks[index]:
+            # The pages that hold a kept start are never given back: the hole begins behind them.
+            kept = self.blocks_for(group.keep_first)
+            if dead > max(request.released_blocks[index], kept):
                 table = request.tables[index]
-                group.pool.free(table[request.released_blocks[index]:dead])
-                for block in range(request.released_blocks[index], dead):
+                start = max(request.released_blocks[index], kept)
+                group.pool.free(table[start:dead])
+                for block in range(start, dead):
                     table[block] = NULL_PAGE
-                request.arrays[index][request.released_blocks[index]:dead] = NULL_PAGE
-                given_back = dead - request.released_blocks[index]
+                request.arrays[index][start:dead] = NULL_PAGE
+                given_back = dead - start
                 request.released_blocks[index] = dead
                 # While its prompt is still being computed the request keeps its claim at what it will
                 # hold at one time: the pages it has just given back stay promised to it, as far as it
@@ -322,7 +345,7 @@ class CacheManager:
                 if request.computed < request.reserve_tokens:
                     bound = self._live_blocks_needed(group, request.reserve_tokens, request.step_tokens)
                     to_come = self.blocks_for(request.reserve_tokens) - len(table)
-                    wanted = min(to_come, max(0, bound - (len(table) - dead)))
+                    wanted = min(to_come, max(0, bound - (len(table) - dead) - min(kept, dead)))
                     if wanted > request.reserved[index]:
                         request.reserved[index] = min(wanted, request.reserved[index] + given_back)
 
@@ -343,10 +366,11 @@ class CacheManager:
             held: dict[int, Hashable] = {}
             for request_id, request in self._requests.items():
                 table = request.tables[index]
-                assert len(table) == self.blocks_for(request.length), "table length does not match the positions"
+                assert len(table) == self.group_blocks_for(group, request.length), "table length does not match the positions"
                 for block, page in enumerate(table):
                     if page == NULL_PAGE:
-                        assert (group.window > 0 or group.chunk > 0) and block < request.released_blocks[index], \
+                        assert ((group.window > 0 or group.chunk > 0)
+                                and self.blocks_for(group.keep_first) <= block < request.released_blocks[index]), \
                             "hole in a table"
                         continue
                     assert 0 < page < group.pool.num_pages, f"page {page} out of range"

@@ -5,6 +5,7 @@ from .fekotar import FekotarConfig
 from .gefovik import GefovikConfig
 from .legelix import LegelixConfig
 from .qwen3 import Qwen3Config
+from .rizovik import RizovikConfig
 from .registry import (ArchitectureEntry, load_model_config, load_model_spec, read_config_json,
                        register_architecture, registered_architectures, resolve_architecture,
                        unregister_architecture)
@@ -13,7 +14,7 @@ from .spec import (FeedForwardSpec, InputSpec, LayerCall, LayerSpec, MixerSpec, 
 
 __all__ = [
     "ArchitectureEntry", "ConfigError", "FekotarConfig", "GefovikConfig", "FeedForwardSpec", "InputSpec", "InvalidArgumentError", "LayerCall", "LayerSpec", "LegelixConfig",
-    "MixerSpec", "ModelSpec", "NormSpec", "OutOfPagesError", "OutputSpec", "PositionSpec", "Qwen3Config", "WeightError",
+    "MixerSpec", "ModelSpec", "NormSpec", "OutOfPagesError", "OutputSpec", "PositionSpec", "Qwen3Config", "RizovikConfig", "WeightError",
     "ZephyrError", "load_model_config", "load_model_spec", "read_config_json", "register_architecture",
     "registered_architectures", "resolve_architecture", "unregister_architecture",
 ]

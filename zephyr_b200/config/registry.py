@@ -20,6 +20,7 @@ from .fekotar import FekotarConfig
 from .gefovik import GefovikConfig
 from .legelix import LegelixConfig
 from .qwen3 import Qwen3Config
+from .rizovik import RizovikConfig
 from .spec import ModelSpec
 
 
@@ -111,3 +112,4 @@ register_architecture(Qwen3Config.model_type, Qwen3Config.architecture, Qwen3Con
 register_architecture(LegelixConfig.model_type, LegelixConfig.architecture, LegelixConfig)
 register_architecture(GefovikConfig.model_type, GefovikConfig.architecture, GefovikConfig)
 register_architecture(FekotarConfig.model_type, FekotarConfig.architecture, FekotarConfig)
+register_architecture(RizovikConfig.model_type, RizovikConfig.architecture, RizovikConfig)

@@ -20,6 +20,16 @@
 // `softcap` > 0 bounds the scaled scores smoothly: s <- softcap * tanh(s / softcap).  `shared_kv`: the
 // cache keeps keys only and they serve as the values too (kd = vd; a page is [nkv][page_size][kd]).
 //
+// A window may keep the first tokens of a sequence for good (`keep_first` = n: key j < n is seen by every
+// later query, at its true position), and may be followed by pooled blocks (`pool` = P: a second paged
+// store holds one entry per block of P positions, entry b standing for positions b P .. b P + P - 1; a
+// query at position i sees entry b if b P + P - 1 <= i - window, that is the first
+// floor((i - window + 1) / P) entries, in the same softmax as the tokens of its window).
+//
+// `cross_values`: every query head's weights are applied to the values of EVERY key/value head, not
+// only its own: the result is [T, nh, nkv, vd] (a mixing of the heads' weights behind the softmax is a
+// linear map of these).  `out_f32`: the result is written as float32 whatever the cache's type.
+//
 // One CTA serves one tile: a run of consecutive new tokens of one request, one key/value head,
 // and a chunk of that head's query heads.  The (token, head) pairs of the tile are dealt to the
 // warps; key/value tiles of 32 positions are staged in shared memory once and used by all pairs.
@@ -47,6 +57,13 @@ struct AttentionArgs {
   float scale;
   float softcap;             // 0: none
   int shared_kv;             // the keys are the values
+  int keep_first;            // with a window: keys below this position stay visible
+  int pool;                  // 0, or the positions per entry of the pooled store
+  const void* pool_cache;    // the pooled store's pages, laid out as kv_cache
+  const int* pool_table;     // [R, pool_max_blocks]
+  int pool_max_blocks, pool_num_pages;
+  int cross_values;          // grid y = nkv * nkv: (key head, value head) pairs; out [T, nh, nkv, vd]
+  int out_f32;
   const float* sinks;        // null, or [nh]: exp(sinks[h]) joins the denominator of head h's softmax
   const float* head_slopes;  // null, or [nh]: query head h adds head_slopes[h] * (key position - query position) to its scores
   int* status;
@@ -61,7 +78,8 @@ template <> struct KPad<__nv_bfloat16> { static constexpr int N = 2; };
 // Rows whose bytes are a multiple of 16 are stored with permuted 16-byte chunks (common.cuh:
 // kv_swizzle) and move as vectors; any other width is stored as it is and moves element by element.
 template <typename T>
-__device__ __forceinline__ void stage_rows(T* dst, int dst_stride, const T* cache, const AttentionArgs& a, int row,
+__device__ __forceinline__ void stage_rows(T* dst, int dst_stride, const T* cache, const int* table, int max_blocks,
+                                           int num_pages, const AttentionArgs& a, int row,
                                            int kvh, int k0, int lo, int hi, int dim, long long page_elems,
                                            long long part, int tok0) {
   constexpr int vec = 16 / static_cast<int>(sizeof(T));
@@ -74,8 +92,8 @@ __device__ __forceinline__ void stage_rows(T* dst, int dst_stride, const T* cach
     long long base = 0;
     if (ok) {
       const int block = pos / a.page_size;
-      const int page = block < a.max_blocks ? a.block_table[static_cast<size_t>(row) * a.max_blocks + block] : -1;
-      if (page <= 0 || page >= a.num_pages) {
+      const int page = block < max_blocks ? table[static_cast<size_t>(row) * max_blocks + block] : -1;
+      if (page <= 0 || page >= num_pages) {
         report(a.status, STATUS_PAGE_OUT_OF_RANGE, page, tok0);
         ok = false;
       } else {
@@ -106,7 +124,9 @@ paged_attention_simt_kernel(const AttentionArgs a) {
   T* v_s = a.shared_kv ? k_s : k_s + ATT_TILE * kstride;                  // [ATT_TILE][vd], or the keys again
   const int vstride = a.shared_kv ? kstride : vd;
 
-  const int tile = blockIdx.x, kvh = blockIdx.y, chunk = blockIdx.z;
+  const int tile = blockIdx.x, chunk = blockIdx.z;
+  const int kvh = a.cross_values ? blockIdx.y % a.nkv : blockIdx.y;      // whose keys
+  const int vh = a.cross_values ? blockIdx.y / a.nkv : kvh;              // whose values
   const int row = a.tile_row[tile], q0 = a.tile_q0[tile];
   if (row < 0 || row >= a.num_rows) {
     if (threadIdx.x == 0) report(a.status, STATUS_ROW_OUT_OF_RANGE, row, tile);
@@ -138,58 +158,85 @@ paged_attention_simt_kernel(const AttentionArgs a) {
     for (int c = 0; c < ACC; ++c) acc[i][c] = 0.0f;
   }
 
-  // Keys any pair of this tile may see: [lo, hi).
+  // Keys any pair of this tile may see: [lo, hi), before them the kept first tokens [0, kept) and the
+  // first `entries` entries of the pooled store.
   const int hi = ctx + q0 + n_tok;
   int lo = a.window > 0 ? max(0, ctx + q0 - a.window + 1) : 0;
   if (a.chunk > 0) lo = max(lo, (ctx + q0) / a.chunk * a.chunk);
+  const int kept = a.window > 0 ? min(a.keep_first, lo) : 0;
+  const int entries = (a.pool > 0 && a.window > 0) ? max(0, (hi - 1 - a.window + 1) / a.pool) : 0;
   const long long page_elems = static_cast<long long>(a.nkv) * a.page_size * (a.shared_kv ? kd : kd + vd);
   const long long value_part = static_cast<long long>(a.nkv) * a.page_size * kd;
 
-  for (int k0 = lo / ATT_TILE * ATT_TILE; k0 < hi; k0 += ATT_TILE) {
-    __syncthreads();     // the previous tile is no longer read (and q_s is complete on the first pass)
-    // Positions outside [lo, hi) hold zeros: a page that was given back, or one that another
-    // request used before, is never read.
-    stage_rows<T>(k_s, kstride, cache, a, row, kvh, k0, lo, hi, kd, page_elems, 0, tok0);
-    if (!a.shared_kv) stage_rows<T>(v_s, vd, cache, a, row, kvh, k0, lo, hi, vd, page_elems, value_part, tok0);
-    __syncthreads();
+  // Three runs of keys share the softmax: pooled entries, kept first tokens, the window.
+  for (int run = 0; run < 3; ++run) {
+    const int run_lo = run == 2 ? lo : 0;
+    const int run_hi = run == 0 ? entries : (run == 1 ? kept : hi);
+    if (run_hi <= run_lo) continue;
+    const T* source = run == 0 ? static_cast<const T*>(a.pool_cache) : cache;
+    const int* table = run == 0 ? a.pool_table : a.block_table;
+    const int max_blocks = run == 0 ? a.pool_max_blocks : a.max_blocks;
+    const int num_pages = run == 0 ? a.pool_num_pages : a.num_pages;
+    for (int k0 = run_lo / ATT_TILE * ATT_TILE; k0 < run_hi; k0 += ATT_TILE) {
+      __syncthreads();     // the previous tile is no longer read (and q_s is complete on the first pass)
+      // Positions outside [run_lo, run_hi) hold zeros: a page that was given back, or one that another
+      // request used before, is never read.
+      stage_rows<T>(k_s, kstride, source, table, max_blocks, num_pages, a, row, kvh, k0, run_lo, run_hi, kd,
+                    page_elems, 0, tok0);
+      if (!a.shared_kv)
+        stage_rows<T>(v_s, vd, source, table, max_blocks, num_pages, a, row, vh, k0, run_lo, run_hi, vd, page_elems,
+                      value_part, tok0);
+      __syncthreads();
 
-    const int kp = k0 + lane;
+      const int kp = k0 + lane;
 #pragma unroll
-    for (int i = 0; i < ATT_PAIRS_PER_WARP; ++i) {
-      const int p = warp + i * ATT_WARPS;
-      if (p >= n_pairs) continue;                       // uniform over the warp
-      const int qpos = ctx + q0 + p / n_heads;
-      const float slope = a.head_slopes != nullptr
-                              ? a.head_slopes[kvh * g + chunk * a.heads_per_chunk + (p - p / n_heads * n_heads)] : 0.0f;
-      int first = a.window > 0 ? max(0, qpos - a.window + 1) : 0;
-      if (a.chunk > 0) first = max(first, qpos / a.chunk * a.chunk);
-      if (k0 > qpos || k0 + ATT_TILE <= first) continue;  // no key of this tile is visible
-      const bool valid = kp <= qpos && kp >= first;
-      float s = 0.0f;
-      const float* qp = q_s + p * kd;
-      const T* kr = k_s + lane * kstride;
-      for (int d = 0; d + 1 < kd; d += 2) {
-        s = fmaf(qp[d], to_float(kr[d]), s);
-        s = fmaf(qp[d + 1], to_float(kr[d + 1]), s);
-      }
-      if (kd & 1) s = fmaf(qp[kd - 1], to_float(kr[kd - 1]), s);
-      s *= a.scale;
-      if (a.softcap > 0.0f) s = a.softcap * tanhf(s / a.softcap);
-      s = valid ? fmaf(slope, static_cast<float>(kp - qpos), s) : -INFINITY;
-      const float new_m = fmaxf(m[i], warp_max(s));      // finite: the tile holds a visible key
-      const float pr = valid ? expf(s - new_m) : 0.0f;
-      const float corr = expf(m[i] - new_m);             // exp(-inf) = 0 on the first tile
-      l[i] = l[i] * corr + warp_sum(pr);
-      m[i] = new_m;
+      for (int i = 0; i < ATT_PAIRS_PER_WARP; ++i) {
+        const int p = warp + i * ATT_WARPS;
+        if (p >= n_pairs) continue;                       // uniform over the warp
+        const int qpos = ctx + q0 + p / n_heads;
+        const float slope = a.head_slopes != nullptr
+                                ? a.head_slopes[kvh * g + chunk * a.heads_per_chunk + (p - p / n_heads * n_heads)] : 0.0f;
+        int first = a.window > 0 ? max(0, qpos - a.window + 1) : 0;
+        if (a.chunk > 0) first = max(first, qpos / a.chunk * a.chunk);
+        bool valid;
+        if (run == 0) {
+          const int seen = max(0, (qpos - a.window + 1) / a.pool);      // entries this query sees
+          if (k0 >= seen) continue;
+          valid = kp < seen;
+        } else if (run == 1) {
+          valid = kp < kept;                                            // below every window of the tile
+        } else {
+          if (k0 > qpos || (k0 + ATT_TILE <= first && k0 >= a.keep_first)) continue;  // no key of this tile is visible
+          valid = kp >= lo && kp <= qpos && (kp >= first || kp < a.keep_first);
+        }
+        float s = 0.0f;
+        const float* qp = q_s + p * kd;
+        const T* kr = k_s + lane * kstride;
+        for (int d = 0; d + 1 < kd; d += 2) {
+          s = fmaf(qp[d], to_float(kr[d]), s);
+          s = fmaf(qp[d + 1], to_float(kr[d + 1]), s);
+        }
+        if (kd & 1) s = fmaf(qp[kd - 1], to_float(kr[kd - 1]), s);
+        s *= a.scale;
+        if (a.softcap > 0.0f) s = a.softcap * tanhf(s / a.softcap);
+        s = valid ? (run == 2 ? fmaf(slope, static_cast<float>(kp - qpos), s) : s) : -INFINITY;
+        const float tile_m = warp_max(s);
+        if (tile_m == -INFINITY) continue;                 // (a tile of the window that this query has passed)
+        const float new_m = fmaxf(m[i], tile_m);
+        const float pr = valid ? expf(s - new_m) : 0.0f;
+        const float corr = expf(m[i] - new_m);             // exp(-inf) = 0 on the first tile
+        l[i] = l[i] * corr + warp_sum(pr);
+        m[i] = new_m;
 #pragma unroll
-      for (int c = 0; c < ACC; ++c) acc[i][c] *= corr;
-      for (int j = 0; j < ATT_TILE; ++j) {
-        const float pj = __shfl_sync(0xffffffffu, pr, j);
-        if (pj == 0.0f) continue;                         // uniform over the warp
+        for (int c = 0; c < ACC; ++c) acc[i][c] *= corr;
+        for (int j = 0; j < ATT_TILE; ++j) {
+          const float pj = __shfl_sync(0xffffffffu, pr, j);
+          if (pj == 0.0f) continue;                         // uniform over the warp
 #pragma unroll
-        for (int c = 0; c < ACC; ++c) {
-          const int d = lane + 32 * c;
-          if (d < vd) acc[i][c] = fmaf(pj, to_float(v_s[j * vstride + d]), acc[i][c]);
+          for (int c = 0; c < ACC; ++c) {
+            const int d = lane + 32 * c;
+            if (d < vd) acc[i][c] = fmaf(pj, to_float(v_s[j * vstride + d]), acc[i][c]);
+          }
         }
       }
     }
@@ -210,10 +257,14 @@ paged_attention_simt_kernel(const AttentionArgs a) {
       denominator = l[i] * keep + expf(sink - top);
     }
     const float inv = denominator > 0.0f ? keep / denominator : 0.0f;   // a fully masked row gives zeros
+    const size_t at = a.cross_values ? (static_cast<size_t>(tok0 + qi) * a.nh + head) * a.nkv + vh
+                                     : static_cast<size_t>(tok0 + qi) * a.nh + head;
 #pragma unroll
     for (int c = 0; c < ACC; ++c) {
       const int d = lane + 32 * c;
-      if (d < vd) out[(static_cast<size_t>(tok0 + qi) * a.nh + head) * vd + d] = from_float<T>(acc[i][c] * inv);
+      if (d >= vd) continue;
+      if (a.out_f32) static_cast<float*>(a.out)[at * vd + d] = acc[i][c] * inv;
+      else out[at * vd + d] = from_float<T>(acc[i][c] * inv);
     }
   }
 }
@@ -227,7 +278,7 @@ int attention_simt_launch(const AttentionArgs& a, int n_tiles, int head_chunks, 
   if (smem > 48 * 1024 &&
       cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
     return ERR_CUDA;
-  kernel<<<dim3(n_tiles, a.nkv, head_chunks), ATT_WARPS * 32, smem, stream>>>(a);
+  kernel<<<dim3(n_tiles, a.cross_values ? a.nkv * a.nkv : a.nkv, head_chunks), ATT_WARPS * 32, smem, stream>>>(a);
   return launch_result();
 }
 
@@ -269,10 +320,14 @@ ZB_API int zb_paged_attention_simt(void* out, const void* q, const void* kv_cach
                                    const int* tile_q0, int n_tiles, int tile_tokens, const int* row_q_start,
                                    const int* row_q_len, const int* row_ctx, int nh, int nkv, int kd, int vd,
                                    int window, int chunk, float scale, float softcap, int shared_kv,
-                                   const float* head_slopes, const float* sinks, int dtype, int* status,
+                                   const float* head_slopes, const float* sinks, int keep_first, int pool,
+                                   const void* pool_cache, const int* pool_table, int pool_max_blocks,
+                                   int pool_num_pages, int cross_values, int out_f32, int dtype, int* status,
                                    void* stream) {
   if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || kd <= 0 || vd <= 0 || page_size <= 0 || n_tiles < 0 || window < 0 ||
-      chunk < 0 || softcap < 0.0f || (shared_kv && kd != vd))
+      chunk < 0 || softcap < 0.0f || (shared_kv && kd != vd) || keep_first < 0 || pool < 0 ||
+      (pool > 0 && (window <= 0 || pool_cache == nullptr || pool_table == nullptr || pool_max_blocks <= 0)) ||
+      (cross_values && shared_kv))
     return ERR_BAD_ARGUMENT;
   if (kd > 768 || vd > 768) return ERR_UNSUPPORTED;
   if (n_tiles == 0) return OK;
@@ -287,6 +342,9 @@ ZB_API int zb_paged_attention_simt(void* out, const void* q, const void* kv_cach
   a.max_blocks = max_blocks; a.page_size = page_size; a.num_pages = num_pages; a.num_rows = num_rows;
   a.nh = nh; a.nkv = nkv; a.kd = kd; a.vd = vd; a.window = window; a.chunk = chunk; a.tile_tokens = tile_tokens;
   a.heads_per_chunk = heads_per_chunk; a.scale = scale; a.softcap = softcap; a.shared_kv = shared_kv; a.head_slopes = head_slopes; a.sinks = sinks;
+  a.keep_first = keep_first; a.pool = pool; a.pool_cache = pool_cache; a.pool_table = pool_table;
+  a.pool_max_blocks = pool_max_blocks; a.pool_num_pages = pool_num_pages; a.cross_values = cross_values;
+  a.out_f32 = out_f32;
   a.status = status;
   auto s = static_cast<cudaStream_t>(stream);
   return dtype == DTYPE_F32 ? attention_simt_dispatch<float>(a, n_tiles, head_chunks, s)

@@ -34,7 +34,14 @@ __device__ __forceinline__ float load_shift(const void* b, int w_dtype, int i) {
 }
 
 __device__ __forceinline__ void layer_norm_stats(const float* row, int H, float eps, float* scratch, float& mean,
-                                                 float& rstd) {
+                                                 float& rstd, bool rms = false) {
+  if (rms) {          // an RMS norm: no mean is taken off, the statistic is the mean square
+    float v = 0.0f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) v = fmaf(row[i], row[i], v);
+    mean = 0.0f;
+    rstd = 1.0f / sqrtf(block_sum(v, scratch) / static_cast<float>(H) + eps);
+    return;
+  }
   float s = 0.0f;
   for (int i = threadIdx.x; i < H; i += blockDim.x) s += row[i];
   mean = block_sum(s, scratch) / static_cast<float>(H);
@@ -60,8 +67,9 @@ __global__ void layer_norm_kernel(T* out, const X* x, const void* w, const void*
 }
 
 // residual += mult * LN(delta; w1, b1); then, if `out`, out = LN(residual; w2, b2), or with a null w2
-// the sum itself in T (what a part that reads the stream unnormed takes).
-template <typename T>
+// the sum itself in T (what a part that reads the stream unnormed takes).  RMS: both norms are RMS norms
+// (x / sqrt(mean(x^2) + eps) * w, no mean taken off, no shift).
+template <typename T, bool RMS>
 __global__ void residual_layer_norm_kernel(float* residual, const T* delta, const void* w1, const void* b1, float mult,
                                            T* out, const void* w2, const void* b2, int w_dtype, float eps1, float eps2,
                                            int H) {
@@ -71,7 +79,7 @@ __global__ void residual_layer_norm_kernel(float* residual, const T* delta, cons
   for (int i = threadIdx.x; i < H; i += blockDim.x) ln_row[i] = to_float(delta[base + i]);
   __syncthreads();
   float mean, rstd;
-  layer_norm_stats(ln_row, H, eps1, scratch, mean, rstd);
+  layer_norm_stats(ln_row, H, eps1, scratch, mean, rstd, RMS);
   for (int i = threadIdx.x; i < H; i += blockDim.x) {
     const float y = fmaf((ln_row[i] - mean) * rstd, load_scale(w1, w_dtype, i), load_shift(b1, w_dtype, i));
     const float r = fmaf(mult, y, residual[base + i]);
@@ -81,7 +89,7 @@ __global__ void residual_layer_norm_kernel(float* residual, const T* delta, cons
   }
   if (out == nullptr || w2 == nullptr) return;
   __syncthreads();
-  layer_norm_stats(ln_row, H, eps2, scratch, mean, rstd);
+  layer_norm_stats(ln_row, H, eps2, scratch, mean, rstd, RMS);
   for (int i = threadIdx.x; i < H; i += blockDim.x)
     out[base + i] = from_float<T>(fmaf((ln_row[i] - mean) * rstd, load_scale(w2, w_dtype, i), load_shift(b2, w_dtype, i)));
 }
@@ -109,7 +117,17 @@ __device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
 }
 
 __device__ __forceinline__ void vec_stats(const float4 (&r)[LN_VEC_ITEMS], int nv, int H, float eps, float* scratch,
-                                          float& mean, float& rstd) {
+                                          float& mean, float& rstd, bool rms = false) {
+  if (rms) {
+    float v = 0.0f;
+#pragma unroll
+    for (int j = 0; j < LN_VEC_ITEMS; ++j)
+      if (static_cast<int>(threadIdx.x) + j * LN_VEC_THREADS < nv)
+        v += (r[j].x * r[j].x + r[j].y * r[j].y) + (r[j].z * r[j].z + r[j].w * r[j].w);
+    mean = 0.0f;
+    rstd = 1.0f / sqrtf(block_sum(v, scratch) / static_cast<float>(H) + eps);
+    return;
+  }
   float s = 0.0f;
 #pragma unroll
   for (int j = 0; j < LN_VEC_ITEMS; ++j)
@@ -152,7 +170,7 @@ layer_norm_vec_kernel(T* out, const X* x, const float* w, const float* b, float 
   }
 }
 
-template <typename T>
+template <typename T, bool RMS>
 __global__ void __launch_bounds__(LN_VEC_THREADS)
 residual_layer_norm_vec_kernel(float* residual, const T* delta, const float* w1, const float* b1, float mult, T* out,
                                const float* w2, const float* b2, float eps1, float eps2, int H) {
@@ -166,7 +184,7 @@ residual_layer_norm_vec_kernel(float* residual, const T* delta, const float* w1,
     if (i < nv) r[j] = load4(delta + base + 4 * i);
   }
   float mean, rstd;
-  vec_stats(r, nv, H, eps1, scratch, mean, rstd);
+  vec_stats(r, nv, H, eps1, scratch, mean, rstd, RMS);
 #pragma unroll
   for (int j = 0; j < LN_VEC_ITEMS; ++j) {
     const int i = threadIdx.x + j * LN_VEC_THREADS;
@@ -178,7 +196,7 @@ residual_layer_norm_vec_kernel(float* residual, const T* delta, const float* w1,
     }
   }
   if (out == nullptr || w2 == nullptr) return;
-  vec_stats(r, nv, H, eps2, scratch, mean, rstd);
+  vec_stats(r, nv, H, eps2, scratch, mean, rstd, RMS);
 #pragma unroll
   for (int j = 0; j < LN_VEC_ITEMS; ++j) {
     const int i = threadIdx.x + j * LN_VEC_THREADS;
@@ -762,7 +780,8 @@ ZB_API int zb_layer_norm(void* out, const void* x, const void* w, const void* b,
   return launch_result();
 }
 
-ZB_API int zb_residual_layer_norm(float* residual, const void* delta, const void* w1, const void* b1, float mult,
+template <bool RMS>
+static int residual_norm_launch(float* residual, const void* delta, const void* w1, const void* b1, float mult,
                                   void* out, const void* w2, const void* b2, int w_dtype, float eps1, float eps2,
                                   int rows, int H, int dtype, void* stream) {
   if (rows < 0 || H <= 0) return ERR_BAD_ARGUMENT;
@@ -774,10 +793,10 @@ ZB_API int zb_residual_layer_norm(float* residual, const void* delta, const void
     const float* f2 = static_cast<const float*>(w2);
     const float* g2 = static_cast<const float*>(b2);
     if (dtype == DTYPE_F32)
-      residual_layer_norm_vec_kernel<float><<<rows, LN_VEC_THREADS, 0, s>>>(
+      residual_layer_norm_vec_kernel<float, RMS><<<rows, LN_VEC_THREADS, 0, s>>>(
           residual, static_cast<const float*>(delta), f1, g1, mult, static_cast<float*>(out), f2, g2, eps1, eps2, H);
     else
-      residual_layer_norm_vec_kernel<__nv_bfloat16><<<rows, LN_VEC_THREADS, 0, s>>>(
+      residual_layer_norm_vec_kernel<__nv_bfloat16, RMS><<<rows, LN_VEC_THREADS, 0, s>>>(
           residual, static_cast<const __nv_bfloat16*>(delta), f1, g1, mult, static_cast<__nv_bfloat16*>(out), f2, g2,
           eps1, eps2, H);
     return launch_result();
@@ -785,17 +804,30 @@ ZB_API int zb_residual_layer_norm(float* residual, const void* delta, const void
   const size_t smem = static_cast<size_t>(H) * sizeof(float);
   const int threads = norm_threads(H);
   if (dtype == DTYPE_F32) {
-    auto kernel = residual_layer_norm_kernel<float>;
+    auto kernel = residual_layer_norm_kernel<float, RMS>;
     if (int rc = allow_shared(kernel, smem)) return rc;
     kernel<<<rows, threads, smem, s>>>(residual, static_cast<const float*>(delta), w1, b1, mult,
                                        static_cast<float*>(out), w2, b2, w_dtype, eps1, eps2, H);
   } else {
-    auto kernel = residual_layer_norm_kernel<__nv_bfloat16>;
+    auto kernel = residual_layer_norm_kernel<__nv_bfloat16, RMS>;
     if (int rc = allow_shared(kernel, smem)) return rc;
     kernel<<<rows, threads, smem, s>>>(residual, static_cast<const __nv_bfloat16*>(delta), w1, b1, mult,
                                        static_cast<__nv_bfloat16*>(out), w2, b2, w_dtype, eps1, eps2, H);
   }
   return launch_result();
+}
+
+ZB_API int zb_residual_layer_norm(float* residual, const void* delta, const void* w1, const void* b1, float mult,
+                                  void* out, const void* w2, const void* b2, int w_dtype, float eps1, float eps2,
+                                  int rows, int H, int dtype, void* stream) {
+  return residual_norm_launch<false>(residual, delta, w1, b1, mult, out, w2, b2, w_dtype, eps1, eps2, rows, H, dtype, stream);
+}
+
+// residual += mult * RMSnorm(delta; w1); then out = RMSnorm(residual; w2), or with a null w2 the sum in delta's type.
+ZB_API int zb_residual_rms_norm(float* residual, const void* delta, const void* w1, float mult, void* out,
+                                const void* w2, int w_dtype, float eps1, float eps2, int rows, int H, int dtype,
+                                void* stream) {
+  return residual_norm_launch<true>(residual, delta, w1, nullptr, mult, out, w2, nullptr, w_dtype, eps1, eps2, rows, H, dtype, stream);
 }
 
 ZB_API int zb_embedding_f32(float* out, void* rounded, const void* table, const int* ids, float scale, int tokens,

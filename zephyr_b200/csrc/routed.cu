@@ -31,13 +31,16 @@ constexpr int ROUTE_WARPS = 4;
 // (`sigmoid_scores`) instead of a softmax over all; a choice limited to groups (the outputs form `groups`
 // equal runs of neighbours; a group's mark is the sum of its `group_top` largest choice values, and only
 // outputs of the `keep` groups with the largest marks can be taken; ties: the lower group); and a
-// multiplier on the weights (`weight_scale`).
+// multiplier on the weights (`weight_scale`); a bias on the logits (`logit_bias`, part of the logit for the
+// choice and for the weight alike); and scores that are the logits themselves (`score_kind` 2): the `top`
+// largest logits are taken and weigh their outputs by the softmax over the taken logits only.
 constexpr int ROUTE_GROUP_TOP_MAX = 4;
+constexpr int SCORES_SOFTMAX = 0, SCORES_SIGMOID = 1, SCORES_TOP_SOFTMAX = 2;
 
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 route_kernel(int* ids, float* weights, const float* logits, long long logits_stride, const float* correction,
-             int tokens, int outputs, int top, int sigmoid_scores, int groups, int keep, int group_top,
-             float weight_scale) {
+             int tokens, int outputs, int top, int score_kind, int groups, int keep, int group_top,
+             float weight_scale, const float* logit_bias) {
   __shared__ float choice_of[ROUTE_WARPS][32 * ROUTE_PER_LANE];
   __shared__ float mark_of[ROUTE_WARPS][32 * ROUTE_PER_LANE];
   const int warp = threadIdx.x >> 5;
@@ -45,18 +48,25 @@ route_kernel(int* ids, float* weights, const float* logits, long long logits_str
   if (t >= tokens) return;
   const float* z = logits + t * logits_stride;
   float s[ROUTE_PER_LANE], c[ROUTE_PER_LANE];
-  if (sigmoid_scores) {
+  const bool biased = logit_bias != nullptr;
+  if (score_kind == SCORES_SIGMOID) {
 #pragma unroll
     for (int i = 0; i < ROUTE_PER_LANE; ++i) {
       const int e = lane + 32 * i;
-      s[i] = e < outputs ? 1.0f / (1.0f + expf(-z[e])) : 0.0f;
+      s[i] = e < outputs ? 1.0f / (1.0f + expf(-(z[e] + (biased ? logit_bias[e] : 0.0f)))) : 0.0f;
+    }
+  } else if (score_kind == SCORES_TOP_SOFTMAX) {
+#pragma unroll
+    for (int i = 0; i < ROUTE_PER_LANE; ++i) {
+      const int e = lane + 32 * i;
+      s[i] = e < outputs ? z[e] + (biased ? logit_bias[e] : 0.0f) : -INFINITY;
     }
   } else {
     float top_z = -INFINITY;
 #pragma unroll
     for (int i = 0; i < ROUTE_PER_LANE; ++i) {
       const int e = lane + 32 * i;
-      s[i] = e < outputs ? z[e] : -INFINITY;
+      s[i] = e < outputs ? z[e] + (biased ? logit_bias[e] : 0.0f) : -INFINITY;
       top_z = fmaxf(top_z, s[i]);
     }
     top_z = warp_max(top_z);
@@ -149,8 +159,19 @@ route_kernel(int* ids, float* weights, const float* logits, long long logits_str
     w = __shfl_sync(0xffffffffu, w, best_e & 31);
     if (lane == 0) {
       ids[static_cast<size_t>(t) * top + j] = best_e;
-      weights[static_cast<size_t>(t) * top + j] = w * weight_scale;
+      weights[static_cast<size_t>(t) * top + j] = score_kind == SCORES_TOP_SOFTMAX ? w : w * weight_scale;
     }
+  }
+  if (score_kind == SCORES_TOP_SOFTMAX && lane == 0) {
+    // The taken logits lie in the order of choice, the largest first: their softmax among themselves.
+    float* w = weights + static_cast<size_t>(t) * top;
+    const float largest = w[0];
+    float sum = 0.0f;
+    for (int j = 0; j < top; ++j) {
+      w[j] = expf(w[j] - largest);
+      sum += w[j];
+    }
+    for (int j = 0; j < top; ++j) w[j] = w[j] / sum * weight_scale;
   }
 }
 
@@ -457,13 +478,15 @@ using namespace zb;
 ZB_API int zb_route_max_outputs() { return 32 * ROUTE_PER_LANE; }
 ZB_API int zb_expert_tile_rows(int dtype) { return dtype == DTYPE_F32 ? TP_BM : TM_BM; }
 
-// sigmoid_scores: 0 softmax over all outputs, 1 the logistic function of each.  groups <= 1: no limit on the
+// sigmoid_scores: 0 softmax over all outputs, 1 the logistic function of each, 2 the logits themselves with
+// the softmax over the taken ones as weights.  logit_bias: null, or one float32 per output.  groups <= 1: no limit on the
 // choice; else the outputs form `groups` equal runs and only the `keep` best runs (by the sum of their
 // `group_top` largest choice values) can be taken from: keep * (outputs / groups) must reach `top`.
-ZB_API int zb_route_grouped(int* ids, float* weights, const float* logits, long long logits_stride,
-                            const float* correction, int tokens, int outputs, int top, int sigmoid_scores, int groups,
-                            int keep, int group_top, float weight_scale, void* stream) {
-  if (tokens < 0 || outputs <= 0 || top <= 0 || top > outputs) return ERR_BAD_ARGUMENT;
+ZB_API int zb_route_biased(int* ids, float* weights, const float* logits, long long logits_stride,
+                           const float* correction, int tokens, int outputs, int top, int sigmoid_scores, int groups,
+                           int keep, int group_top, float weight_scale, const float* logit_bias, void* stream) {
+  if (tokens < 0 || outputs <= 0 || top <= 0 || top > outputs || sigmoid_scores < 0 || sigmoid_scores > 2)
+    return ERR_BAD_ARGUMENT;
   if (groups > 1 && (outputs % groups != 0 || keep <= 0 || keep > groups || group_top <= 0 ||
                      keep * (outputs / groups) < top))
     return ERR_BAD_ARGUMENT;
@@ -471,8 +494,15 @@ ZB_API int zb_route_grouped(int* ids, float* weights, const float* logits, long 
   if (tokens == 0) return OK;
   route_kernel<<<(tokens + ROUTE_WARPS - 1) / ROUTE_WARPS, ROUTE_WARPS * 32, 0, static_cast<cudaStream_t>(stream)>>>(
       ids, weights, logits, logits_stride, correction, tokens, outputs, top, sigmoid_scores, groups, keep, group_top,
-      weight_scale);
+      weight_scale, logit_bias);
   return launch_result();
+}
+
+ZB_API int zb_route_grouped(int* ids, float* weights, const float* logits, long long logits_stride,
+                            const float* correction, int tokens, int outputs, int top, int sigmoid_scores, int groups,
+                            int keep, int group_top, float weight_scale, void* stream) {
+  return zb_route_biased(ids, weights, logits, logits_stride, correction, tokens, outputs, top, sigmoid_scores, groups,
+                         keep, group_top, weight_scale, nullptr, stream);
 }
 
 ZB_API int zb_route(int* ids, float* weights, const float* logits, long long logits_stride, const float* correction,

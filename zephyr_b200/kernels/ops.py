@@ -96,7 +96,26 @@ _SIGNATURES = {
     "zb_attention_simt_tile_tokens": [c_int],
     "zb_paged_attention_simt": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
                                 c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                c_int, c_float, c_float, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
+                                c_int, c_float, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                                c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "zb_qkv_halves": [c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_float, c_void_p, c_int, c_float,
+                      c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                      c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "zb_pool_blocks": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int,
+                       c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "zb_head_mix": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "zb_sigmoid_gate": [c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p],
+    "zb_delta_max_channels": [],
+    "zb_delta_gates": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p,
+                       c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_int,
+                       c_void_p],
+    "zb_delta_scan": [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_longlong,
+                      c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                      c_void_p],
+    "zb_residual_rms_norm": [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_float, c_float, c_int,
+                             c_int, c_int, c_void_p],
+    "zb_route_biased": [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                        c_int, c_float, c_void_p, c_void_p],
     "zb_qkv_pairs": [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_void_p,
                      c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                      c_int, c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p],
@@ -438,6 +457,24 @@ def residual_layer_norm(residual: torch.Tensor, delta: torch.Tensor, w1: torch.T
     _check(library().zb_residual_layer_norm(_ptr(residual), _ptr(delta), _ptr(w1), _ptr(b1), float(mult), _ptr(out),
                                             _ptr(w2), _ptr(b2), 0, float(eps1), float(eps2), rows, H,
                                             DTYPE_CODE[delta.dtype], _stream()), "residual_layer_norm")
+    return out
+
+
+def residual_rms_norm(residual: torch.Tensor, delta: torch.Tensor, w1: torch.Tensor, eps1: float, mult: float,
+                      w2: torch.Tensor | None = None, eps2: float = 0.0, rounded_sum: bool = False) -> torch.Tensor | None:
+    """residual (float32, in place) += mult * RMSnorm(delta; w1); with w2 also returns RMSnorm(residual; w2) in
+    delta's type; with ``rounded_sum`` and no w2 the sum itself in delta's type.  Scales are float32."""
+    _cuda(residual, delta, w1, w2)
+    _require(residual.dim() == 2 and residual.is_contiguous() and residual.dtype == torch.float32
+             and delta.shape == residual.shape and delta.is_contiguous() and delta.dtype in DTYPE_CODE,
+             "a float32 residual [rows, H] and a summand of the same shape")
+    rows, H = residual.shape
+    for vector in (w1, w2):
+        _f32_vector(vector, H, "scales")
+    out = torch.empty_like(delta) if (w2 is not None or rounded_sum) else None
+    _check(library().zb_residual_rms_norm(_ptr(residual), _ptr(delta), _ptr(w1), float(mult), _ptr(out), _ptr(w2), 0,
+                                          float(eps1), float(eps2), rows, H, DTYPE_CODE[delta.dtype], _stream()),
+           "residual_rms_norm")
     return out
 
 
@@ -823,7 +860,10 @@ def paged_attention(q: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.
                     row_ctx: torch.Tensor, nh: int, nkv: int, hd: int, window: int, scale: float,
                     status: torch.Tensor, out: torch.Tensor | None = None,
                     head_slopes: torch.Tensor | None = None, value_dim: int | None = None, chunk: int = 0,
-                    sinks: torch.Tensor | None = None, softcap: float = 0.0, shared_kv: bool = False) -> torch.Tensor:
+                    sinks: torch.Tensor | None = None, softcap: float = 0.0, shared_kv: bool = False,
+                    keep_first: int = 0, pool: int = 0, pool_cache: torch.Tensor | None = None,
+                    pool_table: torch.Tensor | None = None, cross_values: bool = False,
+                    out_dtype: torch.dtype | None = None) -> torch.Tensor:
     """The general kernel: causal attention of every new token over its request's pages.
     ``head_slopes`` (float32 [nh]): query head h adds head_slopes[h] * (key position - query position)
     to its scores, a position encoding that is a bias on the scores.  ``value_dim``: the width of the
@@ -831,8 +871,14 @@ def paged_attention(q: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.
     run of ``chunk`` positions, runs counted from position 0.  ``sinks`` (float32 [nh]): exp(sinks[h])
     joins the denominator of head h's softmax.  ``softcap`` > 0: scaled scores become
     softcap * tanh(score / softcap).  ``shared_kv``: the cache keeps keys only (flat pages
-    [kv_heads * page_size * hd]) and they are the values too."""
-    _cuda(q, kv_cache, block_table, tile_row, tile_q0, row_q_start, row_q_len, row_ctx, status, head_slopes, sinks)
+    [kv_heads * page_size * hd]) and they are the values too.  ``keep_first`` = n (with a window): keys at
+    positions below n stay visible to every later query.  ``pool`` = P (with a window), ``pool_cache`` and
+    ``pool_table``: a second store of one entry per block of P positions; a query at position i also sees
+    the first floor((i - window + 1) / P) entries, in the same softmax.  ``cross_values``: every query
+    head's weights applied to every key/value head's values; the result is [T, nh, nkv, value_dim].
+    ``out_dtype``: float32 for a result that is not rounded to the cache's type."""
+    _cuda(q, kv_cache, block_table, tile_row, tile_q0, row_q_start, row_q_len, row_ctx, status, head_slopes, sinks,
+          pool_cache, pool_table)
     for per_head in (head_slopes, sinks):
         _require(per_head is None or (per_head.dtype == torch.float32 and per_head.is_contiguous()
                                       and per_head.numel() == nh), "one float32 value per query head")
@@ -841,14 +887,149 @@ def paged_attention(q: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.
     _require(q.dim() == 2 and q.is_contiguous() and q.shape[1] == nh * hd and q.dtype in DTYPE_CODE, "q shape")
     _require(not shared_kv or vd == hd, "keys that serve as values have the values' width")
     pages, page_size = _cache_geometry(kv_cache, nkv, hd, 0 if shared_kv else vd, q.dtype)
+    out_dtype = out_dtype or q.dtype
+    _require(out_dtype in (q.dtype, torch.float32), "the result has the queries' type or float32")
+    width = nh * vd * (nkv if cross_values else 1)
     if out is None:
-        out = torch.empty((q.shape[0], nh * vd), dtype=q.dtype, device=q.device)
-    _require(out.shape == (q.shape[0], nh * vd) and out.dtype == q.dtype and out.is_contiguous(), "out must be [T, heads * value_dim]")
+        out = torch.empty((q.shape[0], width), dtype=out_dtype, device=q.device)
+    _require(out.shape == (q.shape[0], width) and out.dtype == out_dtype and out.is_contiguous(), "out must be [T, heads * value_dim]")
+    pool_pages, pool_blocks = 0, 0
+    if pool:
+        _require(window > 0 and pool_cache is not None and pool_table is not None and pool_table.dtype == torch.int32
+                 and pool_table.dim() == 2 and pool_table.shape[0] == block_table.shape[0]
+                 and pool_cache.shape[1:] == kv_cache.shape[1:] and pool_cache.dtype == kv_cache.dtype
+                 and pool_cache.is_contiguous(), "a pooled store has the pages' shape and a table row per request")
+        pool_pages, pool_blocks = pool_cache.shape[0], pool_table.shape[1]
     _check(library().zb_paged_attention_simt(
         _ptr(out), _ptr(q), _ptr(kv_cache), _ptr(block_table), block_table.shape[1], page_size, pages,
         block_table.shape[0], _ptr(tile_row), _ptr(tile_q0), tile_row.numel(), int(tile_tokens), _ptr(row_q_start),
         _ptr(row_q_len), _ptr(row_ctx), nh, nkv, hd, vd, int(window), int(chunk), float(scale), float(softcap),
-        int(shared_kv), _ptr(head_slopes), _ptr(sinks), DTYPE_CODE[q.dtype], _ptr(status), _stream()), "paged_attention")
+        int(shared_kv), _ptr(head_slopes), _ptr(sinks), int(keep_first), int(pool), _ptr(pool_cache),
+        _ptr(pool_table), pool_blocks, pool_pages, int(cross_values), int(out_dtype == torch.float32 and q.dtype != torch.float32),
+        DTYPE_CODE[q.dtype], _ptr(status), _stream()), "paged_attention")
+    return out
+
+
+QK_NORMS = {"none": 0, "per_head": 1, "whole": 2}
+
+
+def qkv_halves(qkv: torch.Tensor, nh: int, nkv: int, kd: int, vd: int, norm: str, q_norm_w: torch.Tensor | None,
+               k_norm_w: torch.Tensor | None, eps: float, freqs: torch.Tensor | None, rot_dims: int, rot_mult: float,
+               value_unit_norm: bool, positions: torch.Tensor, token_row: torch.Tensor, kv_cache: torch.Tensor | None,
+               block_table: torch.Tensor, status: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """From a fused q/k/v projection to queries and cache entries, for a rotation of halves: an RMS norm of q
+    and of k (``norm`` "per_head": per head, scales [kd] shared by the heads; "whole": one statistic over all
+    heads of q and one over all heads of k, scales [nh * kd] and [nkv * kd]; "none"; scales may be None),
+    the rotation of value i with value i + rot_dims / 2 by position * freqs[i] on the first ``rot_dims``
+    values of every q and k head (cosine and sine times ``rot_mult``), every value head divided by its root
+    mean square (``value_unit_norm``), and the cache write of k and v.  Returns the queries [T, nh * kd] in
+    ``dtype``; ``qkv`` may be float32 whatever ``dtype`` is.  Without ``kv_cache`` only the queries are made."""
+    _cuda(qkv, q_norm_w, k_norm_w, freqs, positions, token_row, kv_cache, block_table, status)
+    _i32(positions, token_row, block_table)
+    T = qkv.shape[0]
+    width = nh * kd + (nkv * (kd + vd) if kv_cache is not None else 0)
+    _require(qkv.dim() == 2 and qkv.shape[1] >= width and qkv.stride(1) == 1 and qkv.dtype in DTYPE_CODE,
+             "qkv must be [T, heads*key_dim + kv_heads*(key_dim + value_dim)] with unit inner stride")
+    _require(norm in QK_NORMS, f"the norm of q and k is one of {sorted(QK_NORMS)}")
+    sizes = (nh * kd, nkv * kd) if norm == "whole" else (kd, kd)
+    for vector, size in ((q_norm_w, sizes[0]), (k_norm_w, sizes[1]), (freqs, rot_dims // 2)):
+        _require(vector is None or (vector.dtype == torch.float32 and vector.is_contiguous() and vector.numel() == size),
+                 f"a float32 vector of {size} values")
+    _require(positions.numel() == T and token_row.numel() == T and block_table.dim() == 2, "one position and row per token")
+    pages, page_size = (0, 1)
+    if kv_cache is not None:
+        pages, page_size = _cache_geometry(kv_cache, nkv, kd, vd, dtype)
+    q_out = torch.empty((T, nh * kd), dtype=dtype, device=qkv.device)
+    _check(library().zb_qkv_halves(
+        _ptr(q_out), _ptr(qkv), qkv.stride(0), QK_NORMS[norm], _ptr(q_norm_w), _ptr(k_norm_w), float(eps), _ptr(freqs),
+        int(rot_dims), float(rot_mult), int(value_unit_norm), _ptr(positions), _ptr(token_row), _ptr(kv_cache),
+        _ptr(block_table), block_table.shape[1], page_size, pages, block_table.shape[0], T, nh, nkv, kd, vd,
+        DTYPE_CODE[qkv.dtype], DTYPE_CODE[dtype], _ptr(status), _stream()), "qkv_halves")
+    return q_out
+
+
+def pool_blocks(kv_cache: torch.Tensor, block_table: torch.Tensor, pool_cache: torch.Tensor, pool_table: torch.Tensor,
+                positions: torch.Tensor, token_row: torch.Tensor, nkv: int, kd: int, vd: int, pool: int,
+                status: torch.Tensor) -> None:
+    """For every new token that completes a block of ``pool`` positions (position p with (p + 1) % pool == 0),
+    entry p // pool of the pooled store becomes the mean of the block's keys and values as the pages hold
+    them (float32 sums in the order of the positions, one rounding)."""
+    _cuda(kv_cache, block_table, pool_cache, pool_table, positions, token_row, status)
+    _i32(block_table, pool_table, positions, token_row)
+    pages, page_size = _cache_geometry(kv_cache, nkv, kd, vd, kv_cache.dtype)
+    _require(pool_cache.shape[1:] == kv_cache.shape[1:] and pool_cache.dtype == kv_cache.dtype and pool_cache.is_contiguous()
+             and pool_table.dim() == 2 and pool_table.shape[0] == block_table.shape[0], "a pooled store has the pages' shape")
+    _check(library().zb_pool_blocks(
+        _ptr(kv_cache), _ptr(block_table), block_table.shape[1], pages, _ptr(pool_cache), _ptr(pool_table),
+        pool_table.shape[1], pool_cache.shape[0], _ptr(positions), _ptr(token_row), positions.numel(),
+        block_table.shape[0], page_size, nkv, kd, vd, int(pool), DTYPE_CODE[kv_cache.dtype], _ptr(status), _stream()),
+        "pool_blocks")
+
+
+def head_mix(a: torch.Tensor, mix: torch.Tensor, nh: int, nkv: int, vd: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """out[t, h] = sum_g mix[h, g] * a[t, g, kv(h)]: ``a`` float32 [T, nh * nkv * vd] (what every head's softmax
+    weights make of every key/value head's values), ``mix`` float32 [nh, nh]; the result [T, nh * vd]."""
+    _cuda(a, mix)
+    _require(a.dim() == 2 and a.is_contiguous() and a.dtype == torch.float32 and a.shape[1] == nh * nkv * vd, "a: float32 [T, nh * nkv * vd]")
+    _require(mix.dtype == torch.float32 and mix.is_contiguous() and mix.shape == (nh, nh), "mix: float32 [nh, nh]")
+    out = torch.empty((a.shape[0], nh * vd), dtype=out_dtype, device=a.device)
+    _check(library().zb_head_mix(_ptr(out), _ptr(a), _ptr(mix), a.shape[0], nh, nkv, vd, DTYPE_CODE[out_dtype], _stream()),
+           "head_mix")
+    return out
+
+
+def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+    """x *= sigmoid(gate) in place and value by value; ``gate`` float32 [T, width], rows may be strided."""
+    _cuda(x, gate)
+    _require(x.dim() == 2 and x.is_contiguous() and x.dtype in DTYPE_CODE, "x: contiguous [T, width]")
+    _require(gate.dtype == torch.float32 and gate.shape == x.shape and gate.stride(1) == 1, "gate: float32 [T, width]")
+    _check(library().zb_sigmoid_gate(_ptr(x), _ptr(gate), gate.stride(0), x.shape[0], x.shape[1], DTYPE_CODE[x.dtype],
+                                     _stream()), "sigmoid_gate")
+    return x
+
+
+def delta_max_channels() -> int:
+    return library().zb_delta_max_channels()
+
+
+def delta_rule(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, b: torch.Tensor, a: torch.Tensor,
+               a_log: torch.Tensor, dt_bias: torch.Tensor, heads: int, qk_heads: int, key_dim: int, value_dim: int,
+               state: torch.Tensor, slots: torch.Tensor, row_q_start: torch.Tensor, row_q_len: torch.Tensor,
+               status: torch.Tensor, q_scale: float, unit_eps: float = 1e-6, write_state: bool = True) -> torch.Tensor:
+    """The gated delta rule per head over each row's new tokens, from and to ``state`` [slots, heads *
+    value_dim * key_dim] float32 (rows may be strided; a head's state lies [value_dim][key_dim]):
+    S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q.  q and k [T, qk_heads * key_dim] (head h uses
+    q/k head h // (heads / qk_heads)) are made unit vectors, x / sqrt(sum(x^2) + unit_eps), q times
+    ``q_scale``; v [T, heads * value_dim]; beta = sigmoid(b), g = exp(-exp(a_log) softplus(a + dt_bias)) from
+    float32 b and a [T, heads].  q, k, v share a type and may be strided slices.  Returns o float32
+    [T, heads * value_dim]."""
+    _cuda(q, k, v, b, a, a_log, dt_bias, state, slots, row_q_start, row_q_len, status)
+    _i32(slots, row_q_start, row_q_len)
+    T = v.shape[0]
+    for t, width in ((q, qk_heads * key_dim), (k, qk_heads * key_dim), (v, heads * value_dim)):
+        _require(t.dim() == 2 and t.stride(1) == 1 and t.shape == (T, width) and t.dtype == v.dtype and t.dtype in DTYPE_CODE,
+                 "q, k and v must be [T, .] of one type with unit inner stride")
+    for t in (b, a):
+        _require(t.dim() == 2 and t.shape == (T, heads) and t.dtype == torch.float32 and t.stride(1) == 1
+                 and t.stride(0) == b.stride(0), "b and a: float32 [T, heads] with one row stride")
+    _f32_vector(a_log, heads, "A_log")
+    _f32_vector(dt_bias, heads, "dt_bias")
+    _require(heads % qk_heads == 0, "heads must be a multiple of the q/k heads")
+    _require(state.dim() == 2 and state.dtype == torch.float32 and state.stride(1) == 1
+             and state.shape[1] == heads * key_dim * value_dim, "state must be float32 [slots, heads * value_dim * key_dim]")
+    dev = v.device
+    qn = torch.empty((T, qk_heads * key_dim), dtype=torch.float32, device=dev)
+    kn = torch.empty_like(qn)
+    beta = torch.empty((T, heads), dtype=torch.float32, device=dev)
+    decay = torch.empty_like(beta)
+    _check(library().zb_delta_gates(_ptr(qn), _ptr(kn), _ptr(beta), _ptr(decay), _ptr(q), q.stride(0), _ptr(k), k.stride(0),
+                                    _ptr(b), _ptr(a), b.stride(0), _ptr(a_log), _ptr(dt_bias), T, qk_heads, heads, key_dim,
+                                    float(q_scale), float(unit_eps), DTYPE_CODE[v.dtype], _stream()), "delta_gates")
+    out = torch.empty((T, heads * value_dim), dtype=torch.float32, device=dev)
+    _check(library().zb_delta_scan(_ptr(out), _ptr(qn), _ptr(kn), _ptr(v), v.stride(0), _ptr(beta), _ptr(decay), _ptr(state),
+                                   state.stride(0), _ptr(slots), _ptr(row_q_start), _ptr(row_q_len), slots.numel(), heads,
+                                   heads // qk_heads, key_dim, value_dim, state.shape[0], int(write_state),
+                                   DTYPE_CODE[v.dtype], _ptr(status), _stream()), "delta_scan")
     return out
 
 
@@ -1444,18 +1625,22 @@ def route_max_outputs() -> int:
     return library().zb_route_max_outputs()
 
 
-ROUTE_SCORES = {"softmax": 0, "sigmoid": 1}
+ROUTE_SCORES = {"softmax": 0, "sigmoid": 1, "top_softmax": 2}
 
 
 def route(logits: torch.Tensor, correction: torch.Tensor | None, top: int, scores: str = "softmax",
-          groups: tuple[int, int, int] | None = None, weight_scale: float = 1.0) -> tuple[torch.Tensor, torch.Tensor]:
+          groups: tuple[int, int, int] | None = None, weight_scale: float = 1.0,
+          logit_bias: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
     """Token-choice routing: s = softmax(logits) over all outputs (``scores`` "sigmoid": the logistic function
     of each logit on its own); the ``top`` outputs with the largest s + correction are taken (ties: the lower
     index), each with the weight s * ``weight_scale``.  ``groups`` = (count, keep, group_top): the outputs
     form ``count`` equal runs of neighbours, a run's mark is the sum of its ``group_top`` largest choice
-    values, and only outputs of the ``keep`` runs with the largest marks can be taken.  Returns (ids int32
-    [T, top], weights float32 [T, top]), in the order of choice."""
-    _cuda(logits, correction)
+    values, and only outputs of the ``keep`` runs with the largest marks can be taken.  ``logit_bias``
+    (float32 [outputs]) is added to the logits before anything else.  ``scores`` "top_softmax": the ``top``
+    largest logits are taken and weigh their outputs by the softmax over the taken logits only.  Returns
+    (ids int32 [T, top], weights float32 [T, top]), in the order of choice."""
+    _cuda(logits, correction, logit_bias)
+    _f32_vector(logit_bias, logits.shape[1], "the logits' bias")
     _require(logits.dim() == 2 and logits.dtype == torch.float32 and logits.stride(1) == 1, "float32 logits [T, outputs]")
     _require(scores in ROUTE_SCORES, f"router scores are one of {sorted(ROUTE_SCORES)}")
     T, outputs = logits.shape
@@ -1463,9 +1648,9 @@ def route(logits: torch.Tensor, correction: torch.Tensor | None, top: int, score
     count, keep, group_top = (int(v) for v in groups) if groups is not None else (1, 1, 1)
     ids = torch.empty((T, top), dtype=torch.int32, device=logits.device)
     weights = torch.empty((T, top), dtype=torch.float32, device=logits.device)
-    _check(library().zb_route_grouped(_ptr(ids), _ptr(weights), _ptr(logits), logits.stride(0), _ptr(correction), T,
-                                      outputs, int(top), ROUTE_SCORES[scores], count, keep, group_top,
-                                      float(weight_scale), _stream()), "route")
+    _check(library().zb_route_biased(_ptr(ids), _ptr(weights), _ptr(logits), logits.stride(0), _ptr(correction), T,
+                                     outputs, int(top), ROUTE_SCORES[scores], count, keep, group_top,
+                                     float(weight_scale), _ptr(logit_bias), _stream()), "route")
     return ids, weights
 
 

@@ -22,6 +22,17 @@ normed queries that grows with the position, 1 + coef * ln(floor((p + 1) / every
 (``softcap``).  Any of these sends the layer down the general path: the projection's float32 output
 goes through one kernel (bias, norms, rotation, cache write: ``ops.qkv_pairs``) and the general
 attention kernel, which takes all of them, for prompts and single tokens alike.
+
+A second family of parameters runs through ``ops.qkv_halves`` instead: the rotation of halves on part of a
+head (position kind ``rope_halves``: value i of the first ``dims`` pairs with value i + dims / 2), an RMS norm
+over ALL heads of q and of k at once with a scale per column (``qk_norm`` "whole"; "per_head" is the default),
+values divided by their root mean square per head (``value_unit_norm``), first tokens that a window never
+lets go (``keep_first`` = n: key j < n stays visible, at its true position), pooled blocks behind the window
+(``pool`` = P: the means of the keys and of the values of every whole block of P positions are kept in a
+second store, one entry a block, and a query at position i sees, beside its window, the blocks that end at
+or before i - window, in the same softmax), a mixing of the heads' softmax weights (``head_mix``: a matrix M
+[heads, heads]; head h applies sum_g M[h, g] weights_g to the values of its own key/value head), and a
+sigmoid gate on the joined heads before the output projection (``out_gate``: sigmoid(Wg x), value by value).
 """
 
 from __future__ import annotations
@@ -51,7 +62,7 @@ class Attention(Mixer):
         self.hd = int(p["head_dim"])
         self.window = int(p.get("window", 0))
         self.unit_norm = bool(p.get("unit_qk_norm", False))
-        self.eps = float(p["qk_norm_eps"]) if (p.get("q_norm") or self.unit_norm) else 0.0
+        self.eps = float(p["qk_norm_eps"]) if (p.get("q_norm") or self.unit_norm or p.get("value_unit_norm")) else 0.0
         self.values_from_keys = bool(p.get("values_from_keys", False))
         self.softcap = float(p.get("softcap") or 0.0)
         temp = p.get("q_temp")
@@ -94,10 +105,30 @@ class Attention(Mixer):
         self.sinks = weights[p["sinks"]].float().contiguous() if p.get("sinks") else None
         pairs = getattr(self.position, "as_pair_frequencies", None)
         self.pair_freqs, self.pair_dims = pairs() if pairs is not None else (None, 0)
+        halves = getattr(self.position, "as_half_frequencies", None)
+        self.half_freqs, self.half_dims, self.half_mult = halves() if halves is not None else (None, 0, 1.0)
+        self.qk_norm = str(p.get("qk_norm") or "per_head")
+        self.value_unit_norm = bool(p.get("value_unit_norm", False))
+        self.keep_first = int(p.get("keep_first") or 0)
+        self.pool = int(p.get("pool") or 0)
+        self.head_mix = weights[p["head_mix"]].float().contiguous() if p.get("head_mix") else None
+        self.w_gate = weights[p["out_gate"]] if p.get("out_gate") else None
+        if self.qk_norm not in ("per_head", "whole") or self.keep_first < 0 or self.pool < 0:
+            raise ConfigError("qk_norm is 'per_head' or 'whole'; keep_first and pool are not negative")
+        if (self.keep_first or self.pool) and self.window <= 0:
+            raise ConfigError("kept first tokens and pooled blocks come with a window")
+        # What runs through the kernel that rotates halves.
+        self.halves = (halves is not None or self.qk_norm == "whole" or self.value_unit_norm or self.keep_first > 0
+                       or self.pool > 0 or self.head_mix is not None or self.w_gate is not None)
+        if self.halves and (pairs is not None or self.qkv_bias is not None or self.values_from_keys or self.unit_norm
+                            or self.q_temp is not None):
+            raise ConfigError("the rotation of halves and its companions do not combine with biases, a rotation of "
+                              "adjacent pairs, keys as values, unit norms or a query multiplier")
         # What only the general path takes.
         self.general = (pairs is not None or self.vd != self.hd or self.chunk > 0 or self.sinks is not None
                         or self.qkv_bias is not None or self.o_bias is not None or p.get("scale") is not None
-                        or self.values_from_keys or self.unit_norm or self.softcap > 0.0 or self.q_temp is not None)
+                        or self.values_from_keys or self.unit_norm or self.softcap > 0.0 or self.q_temp is not None
+                        or self.halves)
         if self.general:
             self._init_general(p)
             return
@@ -127,8 +158,12 @@ class Attention(Mixer):
             raise ConfigError("a rotation of adjacent pairs takes even key widths")
         if self.score_slopes_wanted():
             raise ConfigError("a bias on the scores and the general path's extras do not combine")
-        if self.position is not None and self.pair_freqs is None and self.position.as_rotation_tables() != (None, None):
-            raise ConfigError("the general attention path rotates adjacent pairs or nothing")
+        if (self.position is not None and self.pair_freqs is None and self.half_freqs is None
+                and self.position.as_rotation_tables() != (None, None)):
+            raise ConfigError("the general attention path rotates adjacent pairs, halves of part of a head, or nothing")
+        if self.halves and self.w_gate is not None:
+            self.w_qkv = torch.cat([self.w_qkv, self.w_gate], dim=0).contiguous()
+            self.w_q = self.w_qkv[: self.nh * self.hd]
         self.q_norm = self.q_norm.float().contiguous() if self.q_norm is not None else None
         self.k_norm = self.k_norm.float().contiguous() if self.k_norm is not None else None
         self.score_slopes = None
@@ -138,7 +173,7 @@ class Attention(Mixer):
         # The split-context decode kernel and the tensor-core prompt kernel take a chunked mask, sinks and
         # a bound on the scores too, for keys and values of one width in bfloat16; everything else stays
         # with the general kernel.
-        equal = self.vd == self.hd
+        equal = self.vd == self.hd and not (self.keep_first or self.pool or self.head_mix is not None)
         self.fast_decode = equal and ops.paged_decode_supported(self.nh, self.nkv, self.hd, self.dtype)
         self.fast_prefill = equal and ops.paged_prefill_supported(self.nh, self.nkv, self.hd, self.dtype)
         self.prefill_tile_tokens = ops.paged_prefill_tile_tokens()
@@ -159,8 +194,13 @@ class Attention(Mixer):
         if not p.get("values_from_keys"):
             decls[p["v_proj"]] = WeightDecl((nkv * vd, hidden), ROLE_LINEAR)
         if p.get("q_norm"):
-            decls[p["q_norm"]] = WeightDecl((hd,), ROLE_NORM)
-            decls[p["k_norm"]] = WeightDecl((hd,), ROLE_NORM)
+            whole = p.get("qk_norm") == "whole"
+            decls[p["q_norm"]] = WeightDecl((nh * hd if whole else hd,), ROLE_NORM)
+            decls[p["k_norm"]] = WeightDecl((nkv * hd if whole else hd,), ROLE_NORM)
+        if p.get("head_mix"):
+            decls[p["head_mix"]] = WeightDecl((nh, nh), ROLE_LINEAR)
+        if p.get("out_gate"):
+            decls[p["out_gate"]] = WeightDecl((nh * vd, hidden), ROLE_LINEAR)
         for name, size in (("q_bias", nh * hd), ("k_bias", nkv * hd), ("v_bias", nkv * vd), ("o_bias", hidden),
                            ("sinks", nh)):
             if p.get(name) and not (name == "v_bias" and p.get("values_from_keys")):
@@ -168,14 +208,21 @@ class Attention(Mixer):
         return decls
 
     def weights_read(self) -> list[torch.Tensor]:
-        return [t for t in (self.w_qkv, self.w_o, self.q_norm, self.k_norm) if t is not None]
+        return [t for t in (self.w_qkv, self.w_o, self.q_norm, self.k_norm, self.head_mix) if t is not None]
 
     @staticmethod
-    def cache_spec(spec: MixerSpec) -> PagedCacheSpec:
+    def cache_spec(spec: MixerSpec) -> "PagedCacheSpec | tuple":
+        """The tokens' pages; with pooled blocks a second store of one entry per block beside them.  The
+        tokens of a block must outlive the window until their block is whole, so the pages of a pooled
+        layer are given back by the larger of the two."""
         p = spec.params
-        return PagedCacheSpec(int(p["num_kv_heads"]), key_dim=int(p["head_dim"]),
-                              value_dim=int(p.get("value_dim") or p["head_dim"]), window=int(p.get("window", 0)),
-                              chunk=int(p.get("chunk") or 0))
+        window, pool = int(p.get("window", 0)), int(p.get("pool") or 0)
+        sizes = dict(key_dim=int(p["head_dim"]), value_dim=int(p.get("value_dim") or p["head_dim"]))
+        tokens = PagedCacheSpec(int(p["num_kv_heads"]), window=max(window, pool) if window > 0 else 0,
+                                chunk=int(p.get("chunk") or 0), keep_first=int(p.get("keep_first") or 0), **sizes)
+        if pool <= 0:
+            return tokens
+        return tokens, PagedCacheSpec(int(p["num_kv_heads"]), every=pool, **sizes)
 
     @staticmethod
     def tile_requests(spec: MixerSpec) -> list[tuple[int, str]]:
@@ -247,6 +294,17 @@ class Attention(Mixer):
             return out
         which = "multi" if decode_done else ("single" if prefill_done else "all")
         tile_row, tile_q0 = ctx.tiles[(self.tile_tokens, which)]
+        if self.keep_first:
+            masks["keep_first"] = self.keep_first
+        if self.pool:
+            masks.update(pool=self.pool, pool_cache=ctx.caches[call.extra_caches[0]],
+                         pool_table=ctx.block_table(call.extra_caches[0]))
+        if self.head_mix is not None:
+            # Every head's weights on every key/value head's values, unrounded, then the mixing.
+            crossed = ops.paged_attention(q, cache, table, tile_row, tile_q0, self.tile_tokens, ctx.row_q_start,
+                                          ctx.row_q_len, ctx.row_ctx, *common, head_slopes=self.score_slopes,
+                                          value_dim=self.vd, cross_values=True, out_dtype=torch.float32, **masks)
+            return ops.head_mix(crossed, self.head_mix, self.nh, self.nkv, self.vd, q.dtype)
         if tile_row.numel() > 0:
             ops.paged_attention(q, cache, table, tile_row, tile_q0, self.tile_tokens, ctx.row_q_start, ctx.row_q_len,
                                 ctx.row_ctx, *common, out=out, head_slopes=self.score_slopes, value_dim=self.vd, **masks)
@@ -265,11 +323,31 @@ class Attention(Mixer):
             weight, cache = self.w_q, None
             bias = bias[: self.nh * self.hd] if bias is not None else None
         projected = ops.linear(x, weight, out_dtype=torch.float32)
+        if self.halves:
+            return self._forward_halves(projected, ctx, call, cache, table, out_dtype)
         q = ops.qkv_pairs(projected, self.nh, self.nkv, self.hd, self.vd, bias, self.q_norm, self.k_norm, self.eps,
                           self.pair_freqs, self.pair_dims, ctx.positions, ctx.token_row, cache, table, ctx.status,
                           self.dtype, unit_norm=self.unit_norm, values_from_keys=self.values_from_keys,
                           q_temp=self.q_temp)
         attended = self.attend(q, ctx, call)
+        return ops.linear(attended, self.w_o, out_dtype=out_dtype, bias=self.o_bias)
+
+    def _forward_halves(self, projected: torch.Tensor, ctx: StepContext, call: LayerCall, cache, table,
+                        out_dtype: torch.dtype | None) -> torch.Tensor:
+        """Norms, rotation of halves and cache write in one kernel; the blocks that this step's tokens
+        complete are pooled; attention; the gate; the output projection."""
+        if not call.writes_cache and self.w_gate is not None:
+            raise ConfigError("a gated layer that reads another layer's cache is not built")
+        q = ops.qkv_halves(projected, self.nh, self.nkv, self.hd, self.vd, self.qk_norm if self.q_norm is not None else "none",
+                           self.q_norm, self.k_norm, self.eps, self.half_freqs, self.half_dims, self.half_mult,
+                           self.value_unit_norm, ctx.positions, ctx.token_row, cache, table, ctx.status, self.dtype)
+        if self.pool and call.writes_cache:
+            ops.pool_blocks(cache, table, ctx.caches[call.extra_caches[0]], ctx.block_table(call.extra_caches[0]),
+                            ctx.positions, ctx.token_row, self.nkv, self.hd, self.vd, self.pool, ctx.status)
+        attended = self.attend(q, ctx, call)
+        if self.w_gate is not None:
+            at = (self.nh + 2 * self.nkv) * self.hd if self.vd == self.hd else self.nh * self.hd + self.nkv * (self.hd + self.vd)
+            ops.sigmoid_gate(attended, projected[:, at:at + self.nh * self.vd])
         return ops.linear(attended, self.w_o, out_dtype=out_dtype, bias=self.o_bias)
 
     def forward(self, x: torch.Tensor, ctx: StepContext, call: LayerCall,

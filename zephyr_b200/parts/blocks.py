@@ -11,7 +11,7 @@ runs in the same kernel as the norm that follows it where the norms offer that (
 the last one as a ``DeferredSum`` that the next block or the output part takes up.
 
 ``outnorm_residual``: a norm on each part's output only; the parts read the stream itself:
-r = x + mixer_out(mixer(x)); x' = r + ffn_out(ffn(r)).  The stream is float32; in a bfloat16 model the
+r = x + m * mixer_out(mixer(x)); x' = r + m * ffn_out(ffn(r)), m = ``residual_mult`` (1 unless given).  The stream is float32; in a bfloat16 model the
 parts get its rounding, which the kernel that does a sum writes in the same pass.
 
 ``parallel_residual``: one norm, whose output both parts read: h = norm(x); x' = x + (mixer(h) + ffn(h)).
@@ -102,6 +102,7 @@ class OutputNormResidual(Block):
         self.feed_forward = feed_forward
         self.norms = dict(norms)
         self.dtype = norms["mixer_out"].dtype
+        self.mult = float((params or {}).get("residual_mult", 1.0))
 
     def forward(self, stream: ResidualStream, ctx: StepContext, call: LayerCall) -> ResidualStream:
         if stream.pending is not None or stream.hidden.dtype != torch.float32:
@@ -115,10 +116,10 @@ class OutputNormResidual(Block):
         else:
             x = hidden if self.dtype == torch.float32 else hidden.to(self.dtype)
         stream.rounded = None
-        summand = DeferredSum(self.mixer.forward(x, ctx, call), self.norms["mixer_out"], 1.0)
+        summand = DeferredSum(self.mixer.forward(x, ctx, call), self.norms["mixer_out"], self.mult)
         if self.feed_forward is not None:
             x = summand.apply(hidden, rounded=self.dtype)
-            summand = DeferredSum(self.feed_forward.forward(x), self.norms["feed_forward_out"], 1.0)
+            summand = DeferredSum(self.feed_forward.forward(x), self.norms["feed_forward_out"], self.mult)
         stream.deferred = summand
         return stream
 

@@ -156,8 +156,9 @@ def yarn_frequencies(freqs: list[float], dims: int, base: float, factor: float, 
 class RopeHalves(PositionEncoding):
     """Rotation of halves: dimension i of the rotated part pairs with dimension i + dims / 2, i < dims / 2;
     (u, v) -> (u c - v s, v c + u s) with c = m cos(p f_i), s = m sin(p f_i), f_i = base^(-2i / dims).
-    ``params``: base, dims (default: the head size), scaling (None, or factor / original / fast / slow as in
-    ``yarn_frequencies``, which also sets m; m = 1 without).  Frequencies are worked out in double
+    ``params``: base, dims (default: the head size), scaling (None; or factor / original / fast / slow as in
+    ``yarn_frequencies``, which also sets m; or kind "linear" with a factor: every frequency divided by it;
+    m = 1 without YaRN).  Frequencies are worked out in double
     precision on the host and kept as float32; angles are float32 products on the device.  Mixers hand
     frequencies and multiplier to their own kernels (``as_half_frequencies``); ``apply`` is not offered."""
 
@@ -175,7 +176,12 @@ class RopeHalves(PositionEncoding):
         freqs = [base ** (-2.0 * i / dims) for i in range(dims // 2)]
         self.mult = 1.0
         scaling = spec.params.get("scaling")
-        if scaling:
+        if scaling and scaling.get("kind") == "linear":
+            factor = float(scaling["factor"])
+            if not factor > 0.0 or factor == float("inf"):
+                raise ConfigError("linear scaling needs a finite positive factor")
+            freqs = [f / factor for f in freqs]
+        elif scaling:
             factor, original, fast, slow = (float(scaling[k]) for k in ("factor", "original", "fast", "slow"))
             if factor <= 0.0 or original <= 0.0 or fast <= 0.0 or slow <= 0.0:
                 raise ConfigError("YaRN scaling needs positive factor, original, fast and slow")

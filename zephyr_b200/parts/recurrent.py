@@ -21,6 +21,14 @@ dt = softplus(dt + dt_bias) without a clamp; per head a = exp(-exp(A_log) dt), k
 head's group, v = x, and o += D x; o joined over heads times silu(z), then RMS-normed in
 ``norm_groups`` equal parts (the gate comes before the norm), times a scale per column, then Wo.
 
+``gated_delta`` (the gated delta rule): q = Wq h and k = Wk h with ``qk_heads`` heads of ``key_dim``, v = Wv h
+with ``heads`` heads of ``value_dim``; each passes a causal convolution over a few taps per channel (no bias)
+and SiLU; q and k are made unit vectors per head, x / sqrt(sum(x^2) + 1e-6), q also times key_dim^(-1/2);
+beta = sigmoid(Wb h) and g = exp(-exp(A_log) softplus(Wa h + dt_bias)) per head; per head
+S <- g S, u = beta (v - S^T k), S <- S + k u^T, o = S^T q; each head's o is RMS-normed over its value
+channels with one scale vector shared by the heads, the heads are joined, multiplied by silu(Wg h) and
+projected by Wo.  The state and the convolution's last taps - 1 inputs live in the request's slot.
+
 ``parallel``: the sum of several mixers over the same input, each with a weight.  Every branch keeps
 its own store; the call's first cache id goes to the first branch and its ``extra_caches`` to the
 others.
@@ -187,6 +195,81 @@ class Mamba2(Mixer):
         return ops.linear(normed, self.w_o, out_dtype=out_dtype)
 
 
+class GatedDeltaRule(Mixer):
+    graph_safe = True
+    takes_out_dtype = True
+
+    UNIT_EPS = 1e-6      # inside the root of the unit norms of q and k: the design fixes it
+
+    def __init__(self, spec: MixerSpec, weights: Mapping[str, torch.Tensor], dtype: torch.dtype,
+                 device: torch.device | str):
+        p = spec.params
+        self.hidden, self.heads, self.qk_heads = int(p["hidden_size"]), int(p["heads"]), int(p["qk_heads"])
+        self.dim, self.vdim, self.taps = int(p["key_dim"]), int(p["value_dim"]), int(p["conv"])
+        self.eps = float(p["norm_eps"])
+        if min(self.heads, self.qk_heads, self.dim, self.vdim) <= 0 or self.heads % self.qk_heads != 0:
+            raise ConfigError("the delta rule needs positive sizes and heads that are a multiple of the q/k heads")
+        if self.dim > ops.delta_max_channels():
+            raise ConfigError(f"the delta rule takes up to {ops.delta_max_channels()} key channels per head, not {self.dim}")
+        if not 1 <= self.taps <= ops.CONV_MAX_TAPS:
+            raise ConfigError(f"the convolution takes 1 to {ops.CONV_MAX_TAPS} taps")
+        qk, hv = self.qk_heads * self.dim, self.heads * self.vdim
+        self.channels = 2 * qk + hv
+        # One product for everything that reads the input in the model's type: q | k | v | gate; the two
+        # per-head projections that enter the recurrence come out of a second, float32 product.
+        self.w_in = torch.cat([weights[p[n]] for n in ("q", "k", "v", "g")], dim=0).contiguous()
+        self.w_ba = torch.cat([weights[p["b"]], weights[p["a"]]], dim=0).contiguous()
+        self.conv_w = torch.cat([weights[p[n]] for n in ("q_conv", "k_conv", "v_conv")], dim=0).float().contiguous()
+        self.conv_b = torch.zeros(self.channels, dtype=torch.float32, device=self.conv_w.device)
+        self.a_log, self.dt_bias = _vector(weights, p["a_log"]), _vector(weights, p["dt_bias"])
+        self.norm = _vector(weights, p["norm"])
+        self.w_o = weights[p["o"]]
+        self.cuts = (0, qk, 2 * qk, 2 * qk + hv)
+        self.scan_floats = self.heads * self.dim * self.vdim
+
+    @staticmethod
+    def weight_decls(spec: MixerSpec) -> dict[str, WeightDecl]:
+        p = spec.params
+        hidden, heads, taps = int(p["hidden_size"]), int(p["heads"]), int(p["conv"])
+        qk, hv = int(p["qk_heads"]) * int(p["key_dim"]), heads * int(p["value_dim"])
+        return {
+            p["q"]: WeightDecl((qk, hidden), ROLE_LINEAR), p["k"]: WeightDecl((qk, hidden), ROLE_LINEAR),
+            p["v"]: WeightDecl((hv, hidden), ROLE_LINEAR), p["g"]: WeightDecl((hv, hidden), ROLE_LINEAR),
+            p["q_conv"]: WeightDecl((qk, taps), ROLE_LINEAR), p["k_conv"]: WeightDecl((qk, taps), ROLE_LINEAR),
+            p["v_conv"]: WeightDecl((hv, taps), ROLE_LINEAR),
+            p["b"]: WeightDecl((heads, hidden), ROLE_LINEAR), p["a"]: WeightDecl((heads, hidden), ROLE_LINEAR),
+            p["a_log"]: WeightDecl((heads,), ROLE_ZERO), p["dt_bias"]: WeightDecl((heads,), ROLE_ZERO),
+            p["norm"]: WeightDecl((int(p["value_dim"]),), ROLE_NORM), p["o"]: WeightDecl((hidden, hv), ROLE_LINEAR),
+        }
+
+    def weights_read(self) -> list[torch.Tensor]:
+        return [self.w_in, self.w_ba, self.w_o, self.conv_w, self.norm]
+
+    @staticmethod
+    def cache_spec(spec: MixerSpec) -> StateCacheSpec:
+        """The rule's state [heads, value_dim, key_dim] and behind it the convolution's last taps - 1 inputs
+        [taps - 1, channels], as one float32 vector."""
+        p = spec.params
+        channels = 2 * int(p["qk_heads"]) * int(p["key_dim"]) + int(p["heads"]) * int(p["value_dim"])
+        scan = int(p["heads"]) * int(p["key_dim"]) * int(p["value_dim"])
+        return StateCacheSpec(shape=(scan + (int(p["conv"]) - 1) * channels,), dtype="float32")
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, call: LayerCall,
+                out_dtype: torch.dtype | None = None) -> torch.Tensor:
+        c, store = self.cuts, ctx.caches[call.cache]
+        projected = ops.linear(x, self.w_in)             # q | k | v | gate
+        steps = ops.linear(x, self.w_ba, out_dtype=torch.float32)       # b | a
+        mixed = ops.causal_conv_silu(projected, self.channels, self.conv_w, self.conv_b, store[:, self.scan_floats:],
+                                     ctx.state_slots, ctx.row_q_start, ctx.row_q_len, ctx.token_row, ctx.status,
+                                     write_state=call.writes_cache)
+        o = ops.delta_rule(mixed[:, c[0]:c[1]], mixed[:, c[1]:c[2]], mixed[:, c[2]:c[3]], steps[:, :self.heads],
+                           steps[:, self.heads:], self.a_log, self.dt_bias, self.heads, self.qk_heads, self.dim,
+                           self.vdim, store[:, :self.scan_floats], ctx.state_slots, ctx.row_q_start, ctx.row_q_len,
+                           ctx.status, q_scale=self.dim ** -0.5, unit_eps=self.UNIT_EPS, write_state=call.writes_cache)
+        normed = ops.gated_group_rms_norm(o, projected[:, c[3]:], self.norm, self.vdim, self.eps, gate_first=False)
+        return ops.linear(normed, self.w_o, out_dtype=out_dtype)
+
+
 def _check_sizes(heads: int, key_channels: int, value_channels: int) -> None:
     if heads <= 0 or key_channels <= 0 or value_channels <= 0:
         raise ConfigError("a recurrent mixer needs positive head counts and widths")
@@ -261,6 +344,7 @@ def _store_count(sub: MixerSpec) -> int:
     return len(need) if isinstance(need, tuple) else 1
 
 
+register_mixer("gated_delta", GatedDeltaRule)
 register_mixer("gla", GatedLinearAttention)
 register_mixer("mamba2", Mamba2)
 register_mixer("parallel", ParallelMixers)

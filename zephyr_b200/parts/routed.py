@@ -9,7 +9,9 @@
 Further forms, each named by the spec: ``scores`` "sigmoid" (s = sigmoid(z), every output on its own);
 ``groups`` = {count, keep, top}: the outputs form ``count`` equal runs of neighbours, a run's mark is the sum of
 its ``top`` largest choice values, and only outputs of the ``keep`` runs with the largest marks can be taken;
-``weight_scale``: a multiplier on every weight.
+``weight_scale``: a multiplier on every weight; ``router_bias``: a bias b on the logits, z = Wr x + b;
+``scores`` "top_softmax": the ``top`` largest logits are taken, and their outputs count with the softmax over
+the taken logits only.
 
 The first ``experts`` router outputs are gated feed-forwards, expert_e(x) = down_e(act(gate_e x) * (up_e x)),
 without biases; the last ``identity`` outputs are identity experts, expert(x) = x, which have no tensors.
@@ -61,6 +63,7 @@ class RoutedFeedForward(FeedForward):
                 self.groups = (count, keep, group_top)
         self.w_router = weights[p["router"]]
         self.correction = weights[p["correction"]].float().contiguous() if p.get("correction") else None
+        self.router_bias = weights[p["router_bias"]].float().contiguous() if p.get("router_bias") else None
         if outputs > ops.route_max_outputs():
             raise ConfigError(f"the routing kernel takes up to {ops.route_max_outputs()} router outputs, not {outputs}")
         names = p["expert_names"]
@@ -82,6 +85,8 @@ class RoutedFeedForward(FeedForward):
         decls = {p["router"]: WeightDecl((outputs, hidden), ROLE_LINEAR)}
         if p.get("correction"):
             decls[p["correction"]] = WeightDecl((outputs,), ROLE_ZERO)
+        if p.get("router_bias"):
+            decls[p["router_bias"]] = WeightDecl((outputs,), ROLE_ZERO)
         for gate, up, down in p["expert_names"]:
             decls[gate] = WeightDecl((inter, hidden), ROLE_LINEAR)
             decls[up] = WeightDecl((inter, hidden), ROLE_LINEAR)
@@ -93,7 +98,8 @@ class RoutedFeedForward(FeedForward):
 
     def route(self, x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
         logits = ops.linear(x, self.w_router, out_dtype=torch.float32)
-        return ops.route(logits, self.correction, self.top, self.scores, self.groups, self.weight_scale)
+        return ops.route(logits, self.correction, self.top, self.scores, self.groups, self.weight_scale,
+                         logit_bias=self.router_bias)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         ids, weights = self.route(x)
