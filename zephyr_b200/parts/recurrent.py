@@ -215,10 +215,12 @@ class GatedDeltaRule(Mixer):
             raise ConfigError(f"the convolution takes 1 to {ops.CONV_MAX_TAPS} taps")
         qk, hv = self.qk_heads * self.dim, self.heads * self.vdim
         self.channels = 2 * qk + hv
-        # One product for everything that reads the input in the model's type: q | k | v | gate; the two
-        # per-head projections that enter the recurrence come out of a second, float32 product.
-        self.w_in = torch.cat([weights[p[n]] for n in ("q", "k", "v", "g")], dim=0).contiguous()
-        self.w_ba = torch.cat([weights[p["b"]], weights[p["a"]]], dim=0).contiguous()
+        # One product with float32 sums out for everything on the way into the recurrence: q | k | v | b | a
+        # (a unit norm of q and k divides by their length, so where q . k is small a rounding of the
+        # projection or of the convolution's output to bfloat16 would turn the normed read-out by a large
+        # angle); the output gate comes out of a second product, in the model's type.
+        self.w_in = torch.cat([weights[p[n]] for n in ("q", "k", "v", "b", "a")], dim=0).contiguous()
+        self.w_g = weights[p["g"]]
         self.conv_w = torch.cat([weights[p[n]] for n in ("q_conv", "k_conv", "v_conv")], dim=0).float().contiguous()
         self.conv_b = torch.zeros(self.channels, dtype=torch.float32, device=self.conv_w.device)
         self.a_log, self.dt_bias = _vector(weights, p["a_log"]), _vector(weights, p["dt_bias"])
@@ -243,7 +245,7 @@ class GatedDeltaRule(Mixer):
         }
 
     def weights_read(self) -> list[torch.Tensor]:
-        return [self.w_in, self.w_ba, self.w_o, self.conv_w, self.norm]
+        return [self.w_in, self.w_g, self.w_o, self.conv_w, self.norm]
 
     @staticmethod
     def cache_spec(spec: MixerSpec) -> StateCacheSpec:
@@ -257,8 +259,8 @@ class GatedDeltaRule(Mixer):
     def forward(self, x: torch.Tensor, ctx: StepContext, call: LayerCall,
                 out_dtype: torch.dtype | None = None) -> torch.Tensor:
         c, store = self.cuts, ctx.caches[call.cache]
-        projected = ops.linear(x, self.w_in)             # q | k | v | gate
-        steps = ops.linear(x, self.w_ba, out_dtype=torch.float32)       # b | a
+        projected = ops.linear(x, self.w_in, out_dtype=torch.float32)      # q | k | v | b | a
+        steps = projected[:, c[3]:]
         mixed = ops.causal_conv_silu(projected, self.channels, self.conv_w, self.conv_b, store[:, self.scan_floats:],
                                      ctx.state_slots, ctx.row_q_start, ctx.row_q_len, ctx.token_row, ctx.status,
                                      write_state=call.writes_cache)
@@ -266,7 +268,7 @@ class GatedDeltaRule(Mixer):
                            steps[:, self.heads:], self.a_log, self.dt_bias, self.heads, self.qk_heads, self.dim,
                            self.vdim, store[:, :self.scan_floats], ctx.state_slots, ctx.row_q_start, ctx.row_q_len,
                            ctx.status, q_scale=self.dim ** -0.5, unit_eps=self.UNIT_EPS, write_state=call.writes_cache)
-        normed = ops.gated_group_rms_norm(o, projected[:, c[3]:], self.norm, self.vdim, self.eps, gate_first=False)
+        normed = ops.gated_group_rms_norm(o, ops.linear(x, self.w_g), self.norm, self.vdim, self.eps, gate_first=False)
         return ops.linear(normed, self.w_o, out_dtype=out_dtype)
 
 
