@@ -33,9 +33,10 @@ def _attention_case(seed, T, H, G, d, dv, targets, sharp=24.0):
 
 
 def _run_attention(cuda_device, dtype, q, k, v, H, G, page, portions, *, window, pool=0, keep_first=0, mix=None,
-                   norm="none", q_w=None, k_w=None, rot=None, value_norm=False, scale=1.0, eps=1e-6):
+                   norm="none", q_w=None, k_w=None, rot=None, value_norm=False, scale=1.0, eps=1e-6, fast=False):
     """The engine's kernels on one request cut into ``portions``: projection -> norms, rotation, cache write ->
-    pooling of the blocks that became whole -> the general attention kernel (-> the mixing of heads)."""
+    pooling of the blocks that became whole -> the general attention kernel, or with ``fast`` the tensor-core
+    prompt kernel, single tokens included (-> the mixing of heads)."""
     from zephyr_b200.kernels import ops
 
     torch_dtype = DTYPES[dtype]
@@ -70,7 +71,14 @@ def _run_attention(cuda_device, dtype, q, k, v, H, G, page, portions, *, window,
             extra = dict(pool=pool, pool_cache=pool_cache, pool_table=pool_table)
         tile_q0 = torch.arange(0, n, tile, dtype=torch.int32, device=cuda_device)
         args = (qs, cache, table, torch.zeros_like(tile_q0), tile_q0, tile, *rows, H, G, d, window, scale, status)
-        if mix is not None:
+        if fast:
+            wide_q0 = torch.arange(0, n, ops.paged_prefill_tile_tokens(), dtype=torch.int32, device=cuda_device)
+            out = torch.full((n, H * dv * (G if mix is not None else 1)), float("nan"), device=cuda_device,
+                             dtype=torch.float32 if mix is not None else torch_dtype)
+            ops.paged_prefill(qs, cache, table, torch.zeros_like(wide_q0), wide_q0, *rows, H, G, d, window, scale, status, out,
+                              keep_first=keep_first, cross_values=mix is not None, **extra)
+            outs.append(ops.head_mix(out, mix.float().to(cuda_device), H, G, dv, torch_dtype) if mix is not None else out)
+        elif mix is not None:
             crossed = ops.paged_attention(*args, value_dim=dv, keep_first=keep_first, cross_values=True,
                                           out_dtype=torch.float32, **extra)
             outs.append(ops.head_mix(crossed, mix.float().to(cuda_device), H, G, dv, torch_dtype))
@@ -79,6 +87,12 @@ def _run_attention(cuda_device, dtype, q, k, v, H, G, page, portions, *, window,
         at += n
     ops.check_status(status)
     return torch.cat(outs).cpu().double()
+
+
+def _prompt_kernel_takes(H, G, d, dv, dtype):
+    from zephyr_b200.kernels import ops
+
+    return d == dv and ops.paged_prefill_supported(H, G, d, DTYPES[dtype])
 
 
 def _expected_attention(dtype, q, k, v, H, G, visible_tokens, visible_blocks=None, pool=0, mix=None, scale=1.0):
@@ -102,7 +116,8 @@ def _expected_attention(dtype, q, k, v, H, G, visible_tokens, visible_blocks=Non
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("H,G,d,dv,size,pool,page", [(4, 2, 32, 32, 40, 16, 16), (3, 1, 24, 40, 19, 5, 16), (8, 1, 64, 16, 12, 12, 32),
                                                     (2, 2, 16, 48, 40, 64, 16), (6, 3, 128, 128, 70, 8, 64), (5, 1, 20, 20, 1, 1, 16),
-                                                    (17, 1, 16, 16, 33, 3, 16)])
+                                                    (17, 1, 16, 16, 33, 3, 16), (4, 2, 64, 64, 19, 5, 16), (6, 1, 96, 96, 100, 2, 32),
+                                                    (2, 1, 256, 256, 64, 64, 16)])
 def test_a_window_followed_by_pooled_blocks(cuda_device, dtype, H, G, d, dv, size, pool, page):
     """Queries of head 0 point at the last key inside the window, at the first one outside it (which may be
     seen only through its block's mean, or not at all), at a key of the block that has just come into sight, at
@@ -121,6 +136,10 @@ def test_a_window_followed_by_pooled_blocks(cuda_device, dtype, H, G, d, dv, siz
         got = _run_attention(cuda_device, dtype, q, k, v, H, G, page, portions, window=size, pool=pool)
         assert torch.isfinite(got).all()
         assert (got - expected).abs().max() < bound, portions[:3]
+        if _prompt_kernel_takes(H, G, d, dv, dtype):
+            got = _run_attention(cuda_device, dtype, q, k, v, H, G, page, portions, window=size, pool=pool, fast=True)
+            assert torch.isfinite(got).all()
+            assert (got - expected).abs().max() < bound, ("tensor cores", portions[:3])
     # what is pointed at decides: leaving the blocks out, or seeing a block one token early, would not pass
     no_blocks = _expected_attention(dtype, q, k, v, H, G, tokens, torch.zeros_like(blocks), pool)
     early = _expected_attention(dtype, q, k, v, H, G, tokens, pooled_window_mask(T + 1, size, pool)[1][1:, : T // pool], pool)
@@ -132,7 +151,7 @@ def test_a_window_followed_by_pooled_blocks(cuda_device, dtype, H, G, d, dv, siz
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("H,G,d,dv,size,keep,page", [(4, 2, 32, 32, 96, 20, 16), (6, 3, 20, 12, 23, 7, 16), (2, 2, 48, 48, 9, 0, 16),
                                                     (5, 5, 16, 24, 70, 33, 32), (8, 4, 128, 128, 33, 40, 16), (3, 1, 64, 64, 5, 1, 64),
-                                                    (4, 1, 16, 16, 300, 4, 16)])
+                                                    (4, 1, 16, 16, 300, 4, 16), (6, 2, 32, 32, 70, 65, 16), (4, 4, 160, 160, 64, 64, 32)])
 def test_a_window_that_keeps_the_first_tokens_with_mixed_heads(cuda_device, dtype, H, G, d, dv, size, keep, page):
     """Queries of head 0 point at the last kept token, the first one that is not kept, the edges of the window
     and the first token; the heads' weights are mixed by a matrix with entries of both signs, so every head's
@@ -152,6 +171,12 @@ def test_a_window_that_keeps_the_first_tokens_with_mixed_heads(cuda_device, dtyp
         assert (got - expected).abs().max() < bound, portions[:3]
         unmixed = _run_attention(cuda_device, dtype, q, k, v, H, G, page, portions, window=size, keep_first=keep)
         assert (unmixed - plain_heads).abs().max() < bound
+        if _prompt_kernel_takes(H, G, d, dv, dtype):
+            got = _run_attention(cuda_device, dtype, q, k, v, H, G, page, portions, window=size, keep_first=keep, mix=mix, fast=True)
+            assert torch.isfinite(got).all()
+            assert (got - expected).abs().max() < bound, ("tensor cores", portions[:3])
+            unmixed = _run_attention(cuda_device, dtype, q, k, v, H, G, page, portions, window=size, keep_first=keep, fast=True)
+            assert (unmixed - plain_heads).abs().max() < bound
     if keep and size + keep < T - 60:
         assert (_expected_attention(dtype, q, k, v, H, G, kept_window_mask(T, size, keep - 1), mix=mix) - expected).abs().max() > 0.3
         assert (_expected_attention(dtype, q, k, v, H, G, kept_window_mask(T, size, keep + 1), mix=mix) - expected).abs().max() > 0.3

@@ -12,6 +12,14 @@
 // in; probabilities are rounded to bfloat16 for the second product.  Math and masking as in
 // attention_simt.cu (causal, lower-right aligned on the cached context, optional window).
 //
+// Further masks, as in attention_simt.cu: a window that keeps the first tokens (`keep_first`), and a window
+// followed by pooled blocks (`pool`: a second paged store of one entry per block of positions, of which a
+// query at position i sees the first floor((i - window + 1) / pool)).  The tiles of keys then come in three
+// runs that share the softmax: pooled entries, kept first tokens, the window.  `cross_values`: the grid
+// covers every (query head, key/value head) pair and head h's weights are applied to the values of head c,
+// the result being [T, nh, nkv, hd] (what a mixing of the heads' weights behind the softmax is a linear map
+// of); `out_f32` writes the result unrounded.
+//
 // Head sizes: every multiple of 32 up to 256 (a query tile's outputs stay in registers: 16 float32
 // values a thread for every 32 of the head).  A tile may hold a single token (one warp works, the
 // others help to fetch): latent attention serves decoded tokens this way where the split-context
@@ -43,6 +51,13 @@ struct PrefillArgs {
   float softcap_log2;            // > 0: scores are softcap * tanh(scale * s / softcap); this is softcap * log2(e)
   float scale_over_cap;          // scale / softcap
   int keys_only;                 // a page holds keys alone, [nkv][page_size][hd], and they are the values too
+  int keep_first;                // with a window: keys below this position stay visible
+  int pool;                      // 0, or the positions per entry of the pooled store
+  const __nv_bfloat16* pool_cache;   // laid out as kv_cache
+  const int* pool_table;         // [R, pool_max_blocks]
+  int pool_max_blocks, pool_num_pages;
+  int cross_values;              // grid x = nh * nkv: head + nh * value head
+  int out_f32;
   int* status;
 };
 
@@ -60,13 +75,14 @@ paged_prefill_kernel(const PrefillArgs a) {
   // The host lists the tiles by the number of keys they see, fewest first: take the list back to
   // front, and all heads of a tile before the next tile, so that the longest work of the whole
   // launch starts first and the short tiles fill the gaps at the end.
-  const int tile = gridDim.y - 1 - blockIdx.y, head = blockIdx.x;
+  const int tile = gridDim.y - 1 - blockIdx.y, head = blockIdx.x % a.nh;
   const int row = a.tile_row[tile], q0 = a.tile_q0[tile];
   if (row < 0 || row >= a.num_rows) {
     if (threadIdx.x == 0) report(a.status, STATUS_ROW_OUT_OF_RANGE, row, tile);
     return;
   }
   const int g = a.nh / a.nkv, kvh = head / g;
+  const int vh = a.cross_values ? blockIdx.x / a.nh : kvh;        // whose values
   const int q_len = a.row_q_len[row], ctx = a.row_ctx[row], tok0 = a.row_q_start[row] + q0;
   const int n_tok = min(PRE_BM, q_len - q0);
   if (n_tok <= 0) return;
@@ -79,7 +95,13 @@ paged_prefill_kernel(const PrefillArgs a) {
   int lo = a.window > 0 ? max(0, ctx + q0 - a.window + 1) : 0;
   if (a.chunk > 0) lo = max(lo, (ctx + q0) / a.chunk * a.chunk);
   const int first_tile = lo / PRE_BN * PRE_BN;
-  const int n_tiles = (hi - first_tile + PRE_BN - 1) / PRE_BN;
+  // Three runs of tiles: the pooled entries the tile's last query sees, the kept first tokens that lie
+  // below every window of the tile, the window.
+  const int entries = (a.pool > 0 && a.window > 0) ? max(0, (hi - a.window) / a.pool) : 0;
+  const int kept = a.window > 0 ? min(a.keep_first, lo) : 0;
+  const int pool_tiles = (entries + PRE_BN - 1) / PRE_BN, kept_tiles = (kept + PRE_BN - 1) / PRE_BN;
+  const int n_tiles = pool_tiles + kept_tiles + (hi - first_tile + PRE_BN - 1) / PRE_BN;
+  const int* pool_table = a.pool > 0 ? a.pool_table + static_cast<size_t>(row) * a.pool_max_blocks : nullptr;
 
   for (int e = threadIdx.x; e < PRE_BM * CHUNKS; e += PRE_WARPS * 32) {
     const int j = e / CHUNKS, c = (e - j * CHUNKS) * 8;
@@ -89,26 +111,36 @@ paged_prefill_kernel(const PrefillArgs a) {
   auto load_tile = [&](int t) {
     __nv_bfloat16* ks = ring + (t & 1) * STAGE;
     __nv_bfloat16* vs = ks + PRE_BN * KROW;
-    const int k0 = first_tile + t * PRE_BN;
+    const int run = t < pool_tiles ? 0 : (t < pool_tiles + kept_tiles ? 1 : 2);
+    const int k0 = run == 0 ? t * PRE_BN : (run == 1 ? (t - pool_tiles) * PRE_BN
+                                                     : first_tile + (t - pool_tiles - kept_tiles) * PRE_BN);
+    const int run_lo = run == 2 ? lo : 0, run_hi = run == 0 ? entries : (run == 1 ? kept : hi);
+    const __nv_bfloat16* source = run == 0 ? a.pool_cache : a.kv_cache;
+    const int* pages = run == 0 ? pool_table : table;
+    const int max_blocks = run == 0 ? a.pool_max_blocks : a.max_blocks;
+    const int num_pages = run == 0 ? a.pool_num_pages : a.num_pages;
     for (int e = threadIdx.x; e < PRE_BN * CHUNKS; e += PRE_WARPS * 32) {
       const int j = e / CHUNKS, c = (e - j * CHUNKS) * 8;
       const int pos = k0 + j;
-      bool ok = pos >= lo && pos < hi;
-      const __nv_bfloat16* src = a.kv_cache;
+      bool ok = pos >= run_lo && pos < run_hi;
+      const __nv_bfloat16* src = source;
+      const __nv_bfloat16* vsrc = source;
       if (ok) {
         const int block = pos / a.page_size;
-        const int page = block < a.max_blocks ? table[block] : -1;
-        if (page <= 0 || page >= a.num_pages) {
+        const int page = block < max_blocks ? pages[block] : -1;
+        if (page <= 0 || page >= num_pages) {
           report(a.status, STATUS_PAGE_OUT_OF_RANGE, page, tok0);
           ok = false;
         } else {
           // logical chunk c / 8 of the row sits at the permuted chunk (common.cuh: kv_swizzle)
-          src += ((static_cast<long long>(page) * (a.keys_only ? 1 : 2) * a.nkv + kvh) * a.page_size + pos % a.page_size) * HD +
-                 (((c >> 3) ^ kv_swizzle(pos, CHUNKS)) << 3);
+          const long long in_row = ((c >> 3) ^ kv_swizzle(pos, CHUNKS)) << 3;
+          const long long page_heads = static_cast<long long>(page) * (a.keys_only ? 1 : 2) * a.nkv;
+          src += ((page_heads + kvh) * a.page_size + pos % a.page_size) * HD + in_row;
+          vsrc += ((page_heads + (a.keys_only ? kvh : a.nkv + vh)) * a.page_size + pos % a.page_size) * HD + in_row;
         }
       }
       cp_async_16(ks + j * KROW + c, src, ok);
-      cp_async_16(vs + j * KROW + c, ok && !a.keys_only ? src + static_cast<long long>(a.nkv) * a.page_size * HD : src, ok);
+      cp_async_16(vs + j * KROW + c, vsrc, ok);
     }
   };
   load_tile(0);
@@ -139,8 +171,12 @@ paged_prefill_kernel(const PrefillArgs a) {
       for (int ks = 0; ks < HD / 16; ++ks)
         ldmatrix_x4(qa[ks], q_s + (warp_row0 + (lane & 7) + ((lane >> 3) & 1) * 8) * KROW + ks * 16 + (lane >> 4) * 8);
     }
-    const int k0 = first_tile + t * PRE_BN;
-    if (!warp_active || k0 > warp_last_pos || k0 + PRE_BN <= warp_first_visible) continue;   // uniform over the warp
+    const int run = t < pool_tiles ? 0 : (t < pool_tiles + kept_tiles ? 1 : 2);
+    const int k0 = run == 0 ? t * PRE_BN : (run == 1 ? (t - pool_tiles) * PRE_BN
+                                                     : first_tile + (t - pool_tiles - kept_tiles) * PRE_BN);
+    if (!warp_active) continue;                          // uniform over the warp, as are the next two
+    if (run == 0 && k0 >= (warp_last_pos - a.window + 1) / a.pool) continue;
+    if (run == 2 && (k0 > warp_last_pos || (k0 + PRE_BN <= warp_first_visible && k0 >= a.keep_first))) continue;
     const __nv_bfloat16* ks_tile = ring + (t & 1) * STAGE;
     const __nv_bfloat16* vs_tile = ks_tile + PRE_BN * KROW;
 
@@ -164,7 +200,11 @@ paged_prefill_kernel(const PrefillArgs a) {
       for (int c = 0; c < 4; ++c) {
         const int pos = k0 + nt * 8 + quad_col + (c & 1);
         const int qp = qpos[c >> 1];
-        const bool valid = pos <= qp && pos >= lo && (a.window == 0 || pos > qp - a.window) && pos >= chunk_start[c >> 1];
+        const bool valid = run == 0 ? pos < (qp - a.window + 1) / a.pool
+                         : run == 1 ? pos < kept
+                                    : pos <= qp && pos >= lo &&
+                                          (a.window == 0 || pos > qp - a.window || pos < a.keep_first) &&
+                                          pos >= chunk_start[c >> 1];
         const float scaled = a.softcap_log2 > 0.0f ? a.softcap_log2 * tanhf(s[nt][c] * a.scale_over_cap)
                                                    : s[nt][c] * a.scale_log2;
         s[nt][c] = valid ? scaled : -INFINITY;
@@ -227,10 +267,19 @@ paged_prefill_kernel(const PrefillArgs a) {
     if (a.sinks != nullptr)      // one more exponential, relative to the running maximum (both in powers of two)
       denominator += exp2f(a.sinks[head] * 1.4426950408889634f - m_run[h]);
     const float inv = denominator > 0.0f ? 1.0f / denominator : 0.0f;
-    __nv_bfloat16* dst = a.out + (static_cast<size_t>(tok0 + r) * a.nh + head) * HD + quad_col;
+    const size_t at = (a.cross_values ? (static_cast<size_t>(tok0 + r) * a.nh + head) * a.nkv + vh
+                                      : static_cast<size_t>(tok0 + r) * a.nh + head) * HD + quad_col;
+    if (a.out_f32) {
+      float* dst = reinterpret_cast<float*>(a.out) + at;
 #pragma unroll
-    for (int n = 0; n < HD / 8; ++n)
-      *reinterpret_cast<unsigned*>(dst + n * 8) = pack_bf16(o[n][2 * h] * inv, o[n][2 * h + 1] * inv);
+      for (int n = 0; n < HD / 8; ++n)
+        *reinterpret_cast<float2*>(dst + n * 8) = make_float2(o[n][2 * h] * inv, o[n][2 * h + 1] * inv);
+    } else {
+      __nv_bfloat16* dst = a.out + at;
+#pragma unroll
+      for (int n = 0; n < HD / 8; ++n)
+        *reinterpret_cast<unsigned*>(dst + n * 8) = pack_bf16(o[n][2 * h] * inv, o[n][2 * h + 1] * inv);
+    }
   }
 }
 
@@ -240,7 +289,7 @@ int prefill_launch(const PrefillArgs& a, int n_tiles, cudaStream_t stream) {
   auto kernel = paged_prefill_kernel<HD>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
     return ERR_CUDA;
-  kernel<<<dim3(a.nh, n_tiles), PRE_WARPS * 32, smem, stream>>>(a);
+  kernel<<<dim3(a.cross_values ? a.nh * a.nkv : a.nh, n_tiles), PRE_WARPS * 32, smem, stream>>>(a);
   return launch_result();
 }
 
@@ -258,12 +307,18 @@ ZB_API int zb_paged_prefill_supported(int nh, int nkv, int hd, int dtype) {
 
 // Attention of the tiles' tokens over their requests' pages; writes those tokens' rows of `out`.
 // `chunk` and `sinks` as in the general kernel (attention_simt.cu).
-ZB_API int zb_paged_prefill_masked(void* out, const void* q, const void* kv_cache, const int* block_table,
-                                   int max_blocks, int page_size, int num_pages, int num_rows, const int* tile_row,
-                                   const int* tile_q0, int n_tiles, const int* row_q_start, const int* row_q_len,
-                                   const int* row_ctx, int nh, int nkv, int hd, int window, int chunk, float scale,
-                                   float softcap, int keys_only, const float* sinks, int* status, void* stream) {
-  if (n_tiles < 0 || page_size <= 0 || window < 0 || chunk < 0 || softcap < 0.0f) return ERR_BAD_ARGUMENT;
+// `keep_first`, `pool` with its store, `cross_values` and `out_f32` as the comment at the top says.
+ZB_API int zb_paged_prefill_windowed(void* out, const void* q, const void* kv_cache, const int* block_table,
+                                     int max_blocks, int page_size, int num_pages, int num_rows, const int* tile_row,
+                                     const int* tile_q0, int n_tiles, const int* row_q_start, const int* row_q_len,
+                                     const int* row_ctx, int nh, int nkv, int hd, int window, int chunk, float scale,
+                                     float softcap, int keys_only, const float* sinks, int keep_first, int pool,
+                                     const void* pool_cache, const int* pool_table, int pool_max_blocks,
+                                     int pool_num_pages, int cross_values, int out_f32, int* status, void* stream) {
+  if (n_tiles < 0 || page_size <= 0 || window < 0 || chunk < 0 || softcap < 0.0f || keep_first < 0 || pool < 0 ||
+      (pool > 0 && (window <= 0 || pool_cache == nullptr || pool_table == nullptr || pool_max_blocks <= 0 || keys_only)) ||
+      (cross_values && keys_only) || nh * (cross_values ? nkv : 1) > 65535)
+    return ERR_BAD_ARGUMENT;
   if (!zb_paged_prefill_supported(nh, nkv, hd, DTYPE_BF16)) return ERR_UNSUPPORTED;
   if (n_tiles == 0) return OK;
   if (n_tiles > 65535) return ERR_UNSUPPORTED;
@@ -279,6 +334,10 @@ ZB_API int zb_paged_prefill_masked(void* out, const void* q, const void* kv_cach
   a.softcap_log2 = softcap * 1.4426950408889634f;
   a.scale_over_cap = softcap > 0.0f ? scale / softcap : 0.0f;
   a.keys_only = keys_only;
+  a.keep_first = window > 0 ? keep_first : 0; a.pool = pool;
+  a.pool_cache = static_cast<const __nv_bfloat16*>(pool_cache);
+  a.pool_table = pool_table; a.pool_max_blocks = pool_max_blocks; a.pool_num_pages = pool_num_pages;
+  a.cross_values = cross_values; a.out_f32 = out_f32;
   a.status = status;
   auto s = static_cast<cudaStream_t>(stream);
   switch (hd) {
@@ -291,6 +350,16 @@ ZB_API int zb_paged_prefill_masked(void* out, const void* q, const void* kv_cach
     case 224: return prefill_launch<224>(a, n_tiles, s);
     default: return prefill_launch<256>(a, n_tiles, s);
   }
+}
+
+ZB_API int zb_paged_prefill_masked(void* out, const void* q, const void* kv_cache, const int* block_table,
+                                   int max_blocks, int page_size, int num_pages, int num_rows, const int* tile_row,
+                                   const int* tile_q0, int n_tiles, const int* row_q_start, const int* row_q_len,
+                                   const int* row_ctx, int nh, int nkv, int hd, int window, int chunk, float scale,
+                                   float softcap, int keys_only, const float* sinks, int* status, void* stream) {
+  return zb_paged_prefill_windowed(out, q, kv_cache, block_table, max_blocks, page_size, num_pages, num_rows, tile_row,
+                                   tile_q0, n_tiles, row_q_start, row_q_len, row_ctx, nh, nkv, hd, window, chunk, scale,
+                                   softcap, keys_only, sinks, 0, 0, nullptr, nullptr, 0, 0, 0, 0, status, stream);
 }
 
 ZB_API int zb_paged_prefill(void* out, const void* q, const void* kv_cache, const int* block_table, int max_blocks,

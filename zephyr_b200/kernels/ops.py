@@ -144,6 +144,10 @@ _SIGNATURES = {
     "zb_paged_prefill_masked": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                                 c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                                 c_float, c_int, c_void_p, c_void_p, c_void_p],
+    "zb_paged_prefill_windowed": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                                  c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
+                                  c_float, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                  c_void_p, c_void_p],
     "zb_paged_decode_fused": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p,
                               c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                               c_longlong, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_int, c_void_p],
@@ -1285,21 +1289,35 @@ def paged_prefill(q: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.Te
                   tile_q0: torch.Tensor, row_q_start: torch.Tensor, row_q_len: torch.Tensor, row_ctx: torch.Tensor,
                   nh: int, nkv: int, hd: int, window: int, scale: float, status: torch.Tensor,
                   out: torch.Tensor, chunk: int = 0, sinks: torch.Tensor | None = None, softcap: float = 0.0,
-                  keys_only: bool = False) -> torch.Tensor:
+                  keys_only: bool = False, keep_first: int = 0, pool: int = 0, pool_cache: torch.Tensor | None = None,
+                  pool_table: torch.Tensor | None = None, cross_values: bool = False) -> torch.Tensor:
     """Tensor-core attention for rows with several new tokens, cut into tiles of
     ``paged_prefill_tile_tokens()``; writes those tokens' rows of ``out``.  ``chunk``, ``sinks`` and
     ``softcap`` as in ``paged_attention``, ``keys_only`` as its ``shared_kv``.  Head size 128 runs on tcgen05
     with the accumulators in tensor memory (every form but the chunked mask), other sizes and chunked masks
-    on mma.sync."""
-    _cuda(q, kv_cache, block_table, tile_row, tile_q0, row_q_start, row_q_len, row_ctx, status, out)
+    on mma.sync.  ``keep_first``, ``pool`` with its store, and ``cross_values`` (``out`` is then
+    [T, nh * nkv * hd], bfloat16 or float32) as in ``paged_attention``: these run on mma.sync."""
+    _cuda(q, kv_cache, block_table, tile_row, tile_q0, row_q_start, row_q_len, row_ctx, status, out, pool_cache, pool_table)
     _i32(block_table, tile_row, tile_q0, row_q_start, row_q_len, row_ctx)
     _require(q.dim() == 2 and q.is_contiguous() and q.shape[1] == nh * hd and q.dtype == torch.bfloat16, "q shape")
-    _require(out.shape == q.shape and out.dtype == q.dtype and out.is_contiguous(), "out must match q")
+    windowed = bool(keep_first or pool or cross_values)
+    if windowed:
+        _require(out.shape == (q.shape[0], nh * hd * (nkv if cross_values else 1)) and out.is_contiguous()
+                 and out.dtype in ((torch.float32, q.dtype) if cross_values else (q.dtype,)), "out: [T, nh (* nkv) * hd]")
+    else:
+        _require(out.shape == q.shape and out.dtype == q.dtype and out.is_contiguous(), "out must match q")
     pages, page_size = _cache_geometry(kv_cache, nkv, hd, 0, q.dtype) if keys_only else _check_cache(kv_cache, nkv, hd, q.dtype)
     _cuda(sinks)
     _require(sinks is None or (sinks.dtype == torch.float32 and sinks.is_contiguous() and sinks.numel() == nh),
              "one float32 sink per query head")
-    tensor_memory = (USE_TCGEN05_PREFILL and not chunk
+    pool_pages, pool_blocks = 0, 0
+    if pool:
+        _require(window > 0 and not keys_only and pool_cache is not None and pool_table is not None
+                 and pool_table.dtype == torch.int32 and pool_table.dim() == 2 and pool_table.shape[0] == block_table.shape[0]
+                 and pool_cache.shape[1:] == kv_cache.shape[1:] and pool_cache.dtype == kv_cache.dtype
+                 and pool_cache.is_contiguous(), "a pooled store has the pages' shape and a table row per request")
+        pool_pages, pool_blocks = pool_cache.shape[0], pool_table.shape[1]
+    tensor_memory = (USE_TCGEN05_PREFILL and not chunk and not windowed
                      and bool(library().zb_paged_prefill_tc_supported(nh, nkv, hd, DTYPE_CODE[q.dtype], page_size)))
     common = (_ptr(out), _ptr(q), _ptr(kv_cache), _ptr(block_table), block_table.shape[1], page_size, pages,
               block_table.shape[0], _ptr(tile_row), _ptr(tile_q0), tile_row.numel(), _ptr(row_q_start), _ptr(row_q_len),
@@ -1307,6 +1325,11 @@ def paged_prefill(q: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.Te
     if tensor_memory:
         _check(library().zb_paged_prefill_tc_masked(*common, float(scale), float(softcap), int(keys_only), _ptr(sinks),
                                                     _ptr(status), _stream()), "paged_prefill")
+    elif windowed:
+        _check(library().zb_paged_prefill_windowed(*common, int(chunk), float(scale), float(softcap), int(keys_only),
+                                                   _ptr(sinks), int(keep_first), int(pool), _ptr(pool_cache),
+                                                   _ptr(pool_table), pool_blocks, pool_pages, int(cross_values),
+                                                   int(out.dtype == torch.float32), _ptr(status), _stream()), "paged_prefill")
     else:
         _check(library().zb_paged_prefill_masked(*common, int(chunk), float(scale), float(softcap), int(keys_only),
                                                  _ptr(sinks), _ptr(status), _stream()), "paged_prefill")

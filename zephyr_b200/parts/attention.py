@@ -173,8 +173,11 @@ class Attention(Mixer):
         # The split-context decode kernel and the tensor-core prompt kernel take a chunked mask, sinks and
         # a bound on the scores too, for keys and values of one width in bfloat16; everything else stays
         # with the general kernel.
-        equal = self.vd == self.hd and not (self.keep_first or self.pool or self.head_mix is not None)
-        self.fast_decode = equal and ops.paged_decode_supported(self.nh, self.nkv, self.hd, self.dtype)
+        equal = self.vd == self.hd
+        # Kept first tokens, pooled blocks and mixed heads are masks and outputs of the mma.sync prompt kernel
+        # (and of the general one); it then serves single tokens too, as tiles of one token.
+        self.windowed = bool(self.keep_first or self.pool or self.head_mix is not None)
+        self.fast_decode = equal and not self.windowed and ops.paged_decode_supported(self.nh, self.nkv, self.hd, self.dtype)
         self.fast_prefill = equal and ops.paged_prefill_supported(self.nh, self.nkv, self.hd, self.dtype)
         self.prefill_tile_tokens = ops.paged_prefill_tile_tokens()
 
@@ -228,7 +231,8 @@ class Attention(Mixer):
     def tile_requests(spec: MixerSpec) -> list[tuple[int, str]]:
         p = spec.params
         tokens = ops.attention_tile_tokens(int(p["num_heads"]) // int(p["num_kv_heads"]))
-        return [(tokens, "all"), (tokens, "multi"), (tokens, "single"), (ops.paged_prefill_tile_tokens(), "multi")]
+        wide = ops.paged_prefill_tile_tokens()
+        return [(tokens, "all"), (tokens, "multi"), (tokens, "single"), (wide, "multi"), (wide, "all")]
 
     # ------------------------------------------------------------------ forward
     def _store_projected(self, projected: torch.Tensor, ctx: StepContext, call: LayerCall) -> torch.Tensor:
@@ -274,6 +278,8 @@ class Attention(Mixer):
         goes to the general kernel."""
         cache = ctx.caches[call.cache]
         table = ctx.block_table(call.cache)
+        if self.general and self.windowed:
+            return self._attend_windowed(q, ctx, call, cache, table)
         out = torch.empty((q.shape[0], self.nh * self.vd), dtype=q.dtype, device=q.device)
         common = (self.nh, self.nkv, self.hd, self.window, self.scale, ctx.status)
         masks = {"chunk": self.chunk, "sinks": self.sinks} if (self.chunk or self.sinks is not None) else {}
@@ -294,21 +300,37 @@ class Attention(Mixer):
             return out
         which = "multi" if decode_done else ("single" if prefill_done else "all")
         tile_row, tile_q0 = ctx.tiles[(self.tile_tokens, which)]
-        if self.keep_first:
-            masks["keep_first"] = self.keep_first
-        if self.pool:
-            masks.update(pool=self.pool, pool_cache=ctx.caches[call.extra_caches[0]],
-                         pool_table=ctx.block_table(call.extra_caches[0]))
-        if self.head_mix is not None:
-            # Every head's weights on every key/value head's values, unrounded, then the mixing.
-            crossed = ops.paged_attention(q, cache, table, tile_row, tile_q0, self.tile_tokens, ctx.row_q_start,
-                                          ctx.row_q_len, ctx.row_ctx, *common, head_slopes=self.score_slopes,
-                                          value_dim=self.vd, cross_values=True, out_dtype=torch.float32, **masks)
-            return ops.head_mix(crossed, self.head_mix, self.nh, self.nkv, self.vd, q.dtype)
         if tile_row.numel() > 0:
             ops.paged_attention(q, cache, table, tile_row, tile_q0, self.tile_tokens, ctx.row_q_start, ctx.row_q_len,
                                 ctx.row_ctx, *common, out=out, head_slopes=self.score_slopes, value_dim=self.vd, **masks)
         return out
+
+    def _attend_windowed(self, q: torch.Tensor, ctx: StepContext, call: LayerCall, cache, table) -> torch.Tensor:
+        """Attention with kept first tokens, pooled blocks or mixed heads: every row, prompts and single
+        tokens alike, on the mma.sync prompt kernel where it takes the shape (bfloat16, one width for keys
+        and values that is a multiple of 32 up to 256), on the general kernel elsewhere.  With mixed heads
+        the kernel hands out every head's weights on every key/value head's values, unrounded, and a second
+        kernel mixes them."""
+        masks = {"chunk": self.chunk, "sinks": self.sinks, "keep_first": self.keep_first}
+        if self.softcap > 0.0:
+            masks["softcap"] = self.softcap
+        if self.pool:
+            masks.update(pool=self.pool, pool_cache=ctx.caches[call.extra_caches[0]],
+                         pool_table=ctx.block_table(call.extra_caches[0]))
+        mixed = self.head_mix is not None
+        width = self.nh * self.vd * (self.nkv if mixed else 1)
+        out = torch.empty((q.shape[0], width), dtype=torch.float32 if mixed else q.dtype, device=q.device)
+        common = (self.nh, self.nkv, self.hd, self.window, self.scale, ctx.status)
+        if self.fast_prefill:
+            tile_row, tile_q0 = ctx.tiles[(self.prefill_tile_tokens, "all")]
+            ops.paged_prefill(q, cache, table, tile_row, tile_q0, ctx.row_q_start, ctx.row_q_len, ctx.row_ctx, *common,
+                              out=out, cross_values=mixed, **masks)
+        else:
+            tile_row, tile_q0 = ctx.tiles[(self.tile_tokens, "all")]
+            ops.paged_attention(q, cache, table, tile_row, tile_q0, self.tile_tokens, ctx.row_q_start, ctx.row_q_len,
+                                ctx.row_ctx, *common, out=out, value_dim=self.vd, cross_values=mixed,
+                                out_dtype=out.dtype, **masks)
+        return ops.head_mix(out, self.head_mix, self.nh, self.nkv, self.vd, q.dtype) if mixed else out
 
     takes_out_dtype = True
 
