@@ -75,6 +75,22 @@ FEKOTAR_SIZES = {
 }
 
 
+# ``--arch rizovik``: the same for the design whose layers mix attention over a window followed by pooled blocks
+# (whole-projection norms, a gate per value), attention over a window that keeps the first tokens (the heads'
+# weights mixed), and the gated delta rule, each with a routed feed-forward (16 experts, a token takes 4: a
+# layer's active width is ``ff``); two of eight layers run an earlier layer's tensors.  Beside it runs Gefovik,
+# the closest design the engine has (norms behind the parts, routed feed-forwards), with capped attention of the
+# same head counts in every layer and the same routed sizes.
+RIZOVIK_SIZES = {
+    "w1024": dict(width=1024, ff=3072, layers=8, heads=8, kv_heads=4, head_dim=128, window=1024, pool=16, keep_first=64,
+                  delta=dict(heads=8, kv_heads=4, dim=128, vdim=128), experts=16, top=4),
+    "w2048": dict(width=2048, ff=6144, layers=8, heads=16, kv_heads=8, head_dim=128, window=1024, pool=16, keep_first=64,
+                  delta=dict(heads=16, kv_heads=8, dim=128, vdim=128), experts=16, top=4),
+    "w4096": dict(width=4096, ff=12288, layers=8, heads=32, kv_heads=8, head_dim=128, window=1024, pool=16, keep_first=64,
+                  delta=dict(heads=32, kv_heads=8, dim=128, vdim=128), experts=16, top=4),
+}
+
+
 def metric_name(args) -> str:
     """One string for both arms: the driver divides their values only if the strings are equal."""
     return f"decode tok/s @ batch {args.batch}, context {args.context} (Qwen3-{args.shape.upper()} shape)"
@@ -280,6 +296,32 @@ def build_fekotar_pair(size: str, batch: int, context: int):
     return fekotar, gefovik, make
 
 
+def build_rizovik_pair(size: str, batch: int, context: int):
+    """(Rizovik configuration, Gefovik configuration of equal sizes, engine builder) of one entry of ``RIZOVIK_SIZES``."""
+    from zephyr_b200.config import GefovikConfig, RizovikConfig
+
+    z = RIZOVIK_SIZES[size]
+    hd = z["head_dim"]
+    routed = {"kind": "moe", "expert": {"ff": z["ff"] // z["top"]}, "router": {"experts": z["experts"], "top": z["top"]}}
+    sizes = dict(heads=z["heads"], kv_heads=z["kv_heads"], dim=hd, vdim=hd, scale=hd ** -0.5)
+    pooled = {"type": "attention", "mlp": routed,
+              "mixer": dict(sizes, rot={"base": 250000.0, "dims": hd // 2}, mask={"size": z["window"], "pool": z["pool"]})}
+    kept = {"type": "attention_2", "mlp": routed,
+            "mixer": dict(sizes, rot={"base": 50000.0, "dims": hd // 4, "scaling": {"factor": 8.0}},
+                          mask={"size": z["window"], "keep_first": z["keep_first"]})}
+    delta = {"type": "delta", "mlp": routed, "mixer": dict(conv=4, **z["delta"])}
+    six = [pooled, kept, delta, pooled, kept, delta]
+    layers = six + [dict(six[0], weights_of=0), dict(six[1], weights_of=1)]
+    rizovik = RizovikConfig(vocab=32768, width=z["width"], norm_eps=1e-6, residual_mult=0.7, layers=tuple(layers[:z["layers"]]))
+    old_routed = {"kind": "moe", "expert": {"ff": z["ff"] // z["top"]}, "router": {"experts": z["experts"], "identity": 0, "top": z["top"]}}
+    capped = dict(heads=z["heads"], kv_heads=z["kv_heads"], dim=hd, vdim=hd, scale=hd ** -0.5, softcap=50.0,
+                  q_temp={"coef": 0.2, "every": 128})
+    gefovik = GefovikConfig(vocab=32768, width=z["width"], norm_eps=1e-6, embedding_scale=1.0,
+                            layers=tuple({"type": "attention", "mixer": capped, "mlp": old_routed} for _ in range(z["layers"])))
+    _, _, make = build_pair("w2048", batch, context)
+    return rizovik, gefovik, make
+
+
 def run_legelix(args) -> dict:
     """Prefill of 2048 tokens and a decode step of ``--batch`` requests at ``--context``, device-timed, for
     every entry of ``LEGELIX_SIZES`` (or ``GEFOVIK_SIZES``) and for the Qwen3 decoder of equal size beside it."""
@@ -290,7 +332,8 @@ def run_legelix(args) -> dict:
     out = {"arch": args.arch, "batch": args.batch, "context": args.context, "prefill_tokens": PREFILL_TOKENS, "dtype": "bf16",
            "data": "synthetic: seeded random weights and token ids", "sizes": {}}
     table, pair, beside = {"legelix": (LEGELIX_SIZES, build_pair, "qwen3"), "gefovik": (GEFOVIK_SIZES, build_gefovik_pair, "qwen3"),
-                           "fekotar": (FEKOTAR_SIZES, build_fekotar_pair, "gefovik")}[args.arch]
+                           "fekotar": (FEKOTAR_SIZES, build_fekotar_pair, "gefovik"),
+                           "rizovik": (RIZOVIK_SIZES, build_rizovik_pair, "gefovik")}[args.arch]
     for size in (args.sizes.split(",") if args.sizes else table):
         legelix, qwen, make = pair(size, args.batch, args.context)
         row = {}
@@ -592,10 +635,10 @@ def main() -> int:
     parser.add_argument("--no-points", dest="points", action="store_false", help="skip decode at batch 1 and 64")
     parser.add_argument("--own-products", action="store_true",
                         help="with --only: no product on the vendor library (all on this package's tcgen05 kernel)")
-    parser.add_argument("--arch", choices=("qwen3", "legelix", "gefovik", "fekotar"), default="qwen3",
+    parser.add_argument("--arch", choices=("qwen3", "legelix", "gefovik", "fekotar", "rizovik"), default="qwen3",
                         help="legelix, gefovik: prefill and decode of that design at a few layer sizes, beside Qwen3 of equal "
-                             "size; fekotar: the same beside Gefovik of equal size")
-    parser.add_argument("--sizes", default="", help="--arch legelix|gefovik|fekotar: entries of that design's table of sizes, with commas (default: all)")
+                             "size; fekotar, rizovik: the same beside Gefovik of equal size")
+    parser.add_argument("--sizes", default="", help="--arch legelix|gefovik|fekotar|rizovik: entries of that design's table of sizes, with commas (default: all)")
     parser.add_argument("--only", choices=("prefill", "decode"), default=None,
                         help="time only the 2048-token prefill, or only the decode step, and print a short line "
                              "(the program a profiler is pointed at)")
@@ -605,7 +648,7 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
-    if args.arch in ("legelix", "gefovik", "fekotar"):
+    if args.arch in ("legelix", "gefovik", "fekotar", "rizovik"):
         print(json.dumps(run_legelix(args)))
         return 0
     if args.only is not None and args.impl == "ours":

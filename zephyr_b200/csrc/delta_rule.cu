@@ -19,6 +19,7 @@
 //
 // Everything here is float32; the values v are read in the model's type.
 #include "common.cuh"
+#include "mma.cuh"
 
 namespace zb {
 
@@ -86,19 +87,24 @@ struct DeltaScanArgs {
   int* status;
 };
 
-// KPL: key channels a lane holds; L = lanes of a column (a power of two, L * KPL >= D); channel
-// d = l + L * i lies with lane l as its i-th.
-template <typename T, int KPL>
-__global__ void __launch_bounds__(DS_THREADS) delta_scan_kernel(const DeltaScanArgs a, int L) {
+// KPL: key channels a lane holds (a multiple of 4); L: lanes of a column (a power of two, L * KPL >= D);
+// lane l holds the channels l * KPL .. l * KPL + KPL - 1.  Both are compile-time, so every address inside the
+// token loop is a base plus a constant.  Tokens are staged 16 at a time into one of two buffers: while a
+// portion's 16 tokens are worked on, the next 16 are on their way (q and k by 16-byte asynchronous copies
+// where D is a multiple of 4, else by plain loads; v, beta and the decays through registers).  In shared
+// memory a token's q (and k) is L runs of KPL + 4 floats (the 4 keep the lanes' 16-byte loads on separate
+// banks); what lies beyond D is zero, so the token loop needs no bounds.  Inside the 16 tokens a lane holds
+// the NEXT token's k and q in registers while the chain S -> S^T k -> u -> S of the present token runs, and
+// sums its products in four separate sums, so the chain a token adds is the reduction over the L lanes, one
+// multiply-add and the write, not the loads.  k . q is summed over the same lanes beside the two read-outs.
+template <typename T, int KPL, int L, bool ASYNC>
+__global__ void __launch_bounds__(DS_THREADS) delta_scan_kernel(const DeltaScanArgs a) {
   extern __shared__ __align__(16) float ds_smem[];
+  constexpr int RUN = KPL + 4, DP = L * RUN;      // a lane's run and a token's row in shared memory
+  constexpr int cols = DS_THREADS / L;            // value columns of this CTA
+  constexpr int stage_floats = 2 * DS_TOKENS * DP + DS_TOKENS * cols + 2 * DS_TOKENS;
+  // one stage: q [DS_TOKENS][DP], k [DS_TOKENS][DP], v [DS_TOKENS][cols], beta [DS_TOKENS], decay [DS_TOKENS]
   const int D = a.D, V = a.V;
-  float* q_s = ds_smem;                          // [DS_TOKENS][D]
-  float* k_s = q_s + DS_TOKENS * D;              // [DS_TOKENS][D]
-  const int cols = DS_THREADS / L;               // value columns of this CTA
-  float* v_s = k_s + DS_TOKENS * D;              // [DS_TOKENS][cols]
-  float* beta_s = v_s + DS_TOKENS * cols;        // [DS_TOKENS]
-  float* decay_s = beta_s + DS_TOKENS;
-  float* kq_s = decay_s + DS_TOKENS;
 
   const int row = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * cols;
   const int slot = a.slots[row];
@@ -107,76 +113,162 @@ __global__ void __launch_bounds__(DS_THREADS) delta_scan_kernel(const DeltaScanA
     return;
   }
   const int t0 = a.row_q_start[row], n = a.row_q_len[row];
-  const int l = threadIdx.x % L, col = col0 + threadIdx.x / L;
+  const int l = threadIdx.x % L, my_col = threadIdx.x / L, col = col0 + my_col;
   const bool live = col < V;
   const int group = head / a.heads_per_group, qk_heads = a.heads / a.heads_per_group;
   float* mine = a.state + static_cast<long long>(slot) * a.slot_stride +
-                (static_cast<long long>(head) * V + (live ? col : 0)) * D;
+                (static_cast<long long>(head) * V + (live ? col : 0)) * D + l * KPL;
+  const bool state_vectors = ASYNC && reinterpret_cast<uintptr_t>(mine) % 16 == 0;
   float S[KPL];
+  if (state_vectors) {
 #pragma unroll
-  for (int i = 0; i < KPL; ++i) {
-    const int d = l + L * i;
-    S[i] = (live && d < D) ? mine[d] : 0.0f;
-  }
-  const T* v = static_cast<const T*>(a.v);
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int base = 0; base < n; base += DS_TOKENS) {
-    const int nt = min(DS_TOKENS, n - base);
-    __syncthreads();            // the tokens staged before are no longer read
-    for (int e = threadIdx.x; e < nt * D; e += DS_THREADS) {
-      const int j = e / D, d = e - j * D;
-      const long long at = (static_cast<long long>(t0 + base + j) * qk_heads + group) * D + d;
-      q_s[j * D + d] = a.q[at];
-      k_s[j * D + d] = a.k[at];
+    for (int i = 0; i < KPL; i += 4) {
+      float4 x = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      if (live && l * KPL + i < D) x = *reinterpret_cast<const float4*>(mine + i);
+      S[i] = x.x; S[i + 1] = x.y; S[i + 2] = x.z; S[i + 3] = x.w;
     }
-    for (int e = threadIdx.x; e < nt * cols; e += DS_THREADS) {
-      const int j = e / cols, c = e - j * cols;
-      v_s[e] = col0 + c < V ? to_float(v[static_cast<long long>(t0 + base + j) * a.v_stride + head * V + col0 + c]) : 0.0f;
+  } else {
+#pragma unroll
+    for (int i = 0; i < KPL; ++i) S[i] = (live && l * KPL + i < D) ? mine[i] : 0.0f;
+  }
+  for (int e = threadIdx.x; e < 2 * stage_floats; e += DS_THREADS) ds_smem[e] = 0.0f;
+  __syncthreads();
+  const T* v = static_cast<const T*>(a.v);
+  const int chunks = (n + DS_TOKENS - 1) / DS_TOKENS;
+  const int vec = D / 4;                         // 16-byte pieces of a row of q or k (ASYNC: D % 4 == 0)
+
+  auto fetch_v = [&](int base, int nt, int e) -> float {
+    const int j = e / cols, c = e - j * cols;
+    return (j < nt && col0 + c < V)
+               ? to_float(v[static_cast<long long>(t0 + base + j) * a.v_stride + head * V + col0 + c]) : 0.0f;
+  };
+  auto issue_qk = [&](int base, int nt, float* stage) {
+    float* q_s = stage;
+    float* k_s = stage + DS_TOKENS * DP;
+    if (ASYNC) {
+      for (int e = threadIdx.x; e < nt * vec; e += DS_THREADS) {
+        const int j = e / vec, c = (e - j * vec) * 4;
+        const long long at = (static_cast<long long>(t0 + base + j) * qk_heads + group) * D + c;
+        const int to = j * DP + (c / KPL) * RUN + c % KPL;
+        cp_async_16(q_s + to, a.q + at, true);
+        cp_async_16(k_s + to, a.k + at, true);
+      }
+    } else {
+      for (int e = threadIdx.x; e < nt * D; e += DS_THREADS) {
+        const int j = e / D, d = e - j * D;
+        const long long at = (static_cast<long long>(t0 + base + j) * qk_heads + group) * D + d;
+        const int to = j * DP + (d / KPL) * RUN + d % KPL;
+        q_s[to] = a.q[at];
+        k_s[to] = a.k[at];
+      }
+    }
+    cp_async_commit();
+  };
+  constexpr int V_PER = (DS_TOKENS * cols + DS_THREADS - 1) / DS_THREADS;
+  float v_next[V_PER], beta_next = 0.0f, decay_next = 0.0f;
+  auto fetch_rest = [&](int base, int nt) {
+#pragma unroll
+    for (int r = 0; r < V_PER; ++r) {
+      const int e = threadIdx.x + r * DS_THREADS;
+      v_next[r] = e < DS_TOKENS * cols ? fetch_v(base, nt, e) : 0.0f;
     }
     if (threadIdx.x < nt) {
-      beta_s[threadIdx.x] = a.beta[static_cast<long long>(t0 + base + threadIdx.x) * a.heads + head];
-      decay_s[threadIdx.x] = a.decay[static_cast<long long>(t0 + base + threadIdx.x) * a.heads + head];
+      beta_next = a.beta[static_cast<long long>(t0 + base + threadIdx.x) * a.heads + head];
+      decay_next = a.decay[static_cast<long long>(t0 + base + threadIdx.x) * a.heads + head];
     }
-    __syncthreads();
-    for (int j = warp; j < nt; j += DS_THREADS / 32) {      // k . q of every staged token, in lane order
-      float s = 0.0f;
-      for (int d = lane; d < D; d += 32) s = fmaf(k_s[j * D + d], q_s[j * D + d], s);
-      s = warp_sum(s);
-      if (lane == 0) kq_s[j] = s;
-    }
-    __syncthreads();
-    for (int j = 0; j < nt; ++j) {
-      const float* kj = k_s + j * D;
-      const float* qj = q_s + j * D;
-      float rk = 0.0f, rq = 0.0f;
+  };
+  auto store_rest = [&](float* stage) {
+    float* v_s = stage + 2 * DS_TOKENS * DP;
 #pragma unroll
-      for (int i = 0; i < KPL; ++i) {
-        const int d = l + L * i;
-        if (d < D) {
-          rk = fmaf(S[i], kj[d], rk);
-          rq = fmaf(S[i], qj[d], rq);
-        }
-      }
-      for (int o = L >> 1; o > 0; o >>= 1) {
-        rk += __shfl_xor_sync(0xffffffffu, rk, o);
-        rq += __shfl_xor_sync(0xffffffffu, rq, o);
-      }
-      const float g = decay_s[j];
-      const float u = beta_s[j] * (v_s[j * cols + threadIdx.x / L] - g * rk);
-#pragma unroll
-      for (int i = 0; i < KPL; ++i) {
-        const int d = l + L * i;
-        if (d < D) S[i] = fmaf(kj[d], u, g * S[i]);
-      }
-      if (l == 0 && live)
-        a.out[static_cast<long long>(t0 + base + j) * a.heads * V + head * V + col] = fmaf(u, kq_s[j], g * rq);
+    for (int r = 0; r < V_PER; ++r) {
+      const int e = threadIdx.x + r * DS_THREADS;
+      if (e < DS_TOKENS * cols) v_s[e] = v_next[r];
     }
-  }
-  if (a.write_state && live) {
+    if (threadIdx.x < DS_TOKENS) {
+      v_s[DS_TOKENS * cols + threadIdx.x] = beta_next;
+      v_s[DS_TOKENS * cols + DS_TOKENS + threadIdx.x] = decay_next;
+    }
+  };
+  auto load_run = [&](float (&x)[KPL], const float* from) {
+#pragma unroll
+    for (int i = 0; i < KPL; i += 4) {
+      const float4 r = *reinterpret_cast<const float4*>(from + i);
+      x[i] = r.x; x[i + 1] = r.y; x[i + 2] = r.z; x[i + 3] = r.w;
+    }
+  };
+  float* out = a.out + static_cast<long long>(t0) * a.heads * V + head * V + col;
+  const long long out_stride = static_cast<long long>(a.heads) * V;
+  // One token: the read-outs of the old state, the write, the output.
+  auto token = [&](const float (&kr)[KPL], const float (&qr)[KPL], float g, float beta, float vj, long long at) {
+    float rk[4] = {0.0f, 0.0f, 0.0f, 0.0f}, rq[4] = {0.0f, 0.0f, 0.0f, 0.0f}, kq[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
     for (int i = 0; i < KPL; ++i) {
-      const int d = l + L * i;
-      if (d < D) mine[d] = S[i];
+      rk[i & 3] = fmaf(S[i], kr[i], rk[i & 3]);
+      rq[i & 3] = fmaf(S[i], qr[i], rq[i & 3]);
+      kq[i & 3] = fmaf(kr[i], qr[i], kq[i & 3]);
+    }
+    float sk = (rk[0] + rk[1]) + (rk[2] + rk[3]), sq = (rq[0] + rq[1]) + (rq[2] + rq[3]);
+    float skq = (kq[0] + kq[1]) + (kq[2] + kq[3]);
+#pragma unroll
+    for (int o = L >> 1; o > 0; o >>= 1) {
+      sk += __shfl_xor_sync(0xffffffffu, sk, o);
+      sq += __shfl_xor_sync(0xffffffffu, sq, o);
+      skq += __shfl_xor_sync(0xffffffffu, skq, o);
+    }
+    const float u = beta * (vj - g * sk);
+#pragma unroll
+    for (int i = 0; i < KPL; ++i) S[i] = fmaf(kr[i], u, g * S[i]);
+    if (l == 0 && live) out[at * out_stride] = fmaf(u, skq, g * sq);
+  };
+
+  if (chunks > 0) {
+    issue_qk(0, min(DS_TOKENS, n), ds_smem);
+    fetch_rest(0, min(DS_TOKENS, n));
+    store_rest(ds_smem);
+  }
+  for (int chunk = 0; chunk < chunks; ++chunk) {
+    const int base = chunk * DS_TOKENS, nt = min(DS_TOKENS, n - base);
+    float* stage = ds_smem + (chunk & 1) * stage_floats;
+    float* other = ds_smem + ((chunk + 1) & 1) * stage_floats;
+    cp_async_wait<0>();
+    __syncthreads();             // this portion has landed, and the other buffer is no longer read
+    const bool more = chunk + 1 < chunks;
+    if (more) {
+      issue_qk(base + DS_TOKENS, min(DS_TOKENS, n - base - DS_TOKENS), other);
+      fetch_rest(base + DS_TOKENS, min(DS_TOKENS, n - base - DS_TOKENS));
+    }
+    const float* q_s = stage + l * RUN;
+    const float* k_s = stage + DS_TOKENS * DP + l * RUN;
+    const float* v_s = stage + 2 * DS_TOKENS * DP + my_col;
+    const float* beta_s = stage + 2 * DS_TOKENS * DP + DS_TOKENS * cols;
+    const float* decay_s = beta_s + DS_TOKENS;
+    // Tokens in pairs: while one token's chain runs on one set of registers, the next token's k and q are
+    // fetched into the other set.
+    float k0[KPL], q0[KPL], k1[KPL], q1[KPL];
+    load_run(k0, k_s);
+    load_run(q0, q_s);
+    for (int j = 0; j < nt; j += 2) {
+      const int j1 = j + 1 < DS_TOKENS ? j + 1 : j, j2 = j + 2 < DS_TOKENS ? j + 2 : j;
+      load_run(k1, k_s + j1 * DP);
+      load_run(q1, q_s + j1 * DP);
+      token(k0, q0, decay_s[j], beta_s[j], v_s[j * cols], base + j);
+      if (j + 1 >= nt) break;
+      load_run(k0, k_s + j2 * DP);
+      load_run(q0, q_s + j2 * DP);
+      token(k1, q1, decay_s[j + 1], beta_s[j + 1], v_s[(j + 1) * cols], base + j + 1);
+    }
+    if (more) store_rest(other);
+  }
+  cp_async_wait<0>();
+  if (a.write_state && live) {
+    if (state_vectors) {
+#pragma unroll
+      for (int i = 0; i < KPL; i += 4)
+        if (l * KPL + i < D) *reinterpret_cast<float4*>(mine + i) = make_float4(S[i], S[i + 1], S[i + 2], S[i + 3]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < KPL; ++i)
+        if (l * KPL + i < D) mine[i] = S[i];
     }
   }
 }
@@ -203,16 +295,31 @@ ZB_API int zb_delta_gates(float* q_out, float* k_out, float* beta, float* decay,
   return launch_result();
 }
 
-template <typename T, int KPL>
-static int delta_scan_launch(const DeltaScanArgs& a, int L, int rows, cudaStream_t s) {
-  const int cols = DS_THREADS / L;
-  const size_t smem = sizeof(float) * (2 * DS_TOKENS * a.D + DS_TOKENS * cols + 3 * DS_TOKENS);
-  auto kernel = delta_scan_kernel<T, KPL>;
+template <typename T, int KPL, int L>
+static int delta_scan_launch(const DeltaScanArgs& a, int rows, cudaStream_t s) {
+  constexpr int cols = DS_THREADS / L;
+  const size_t smem = 2 * sizeof(float) * (2 * DS_TOKENS * L * (KPL + 4) + DS_TOKENS * cols + 2 * DS_TOKENS);
+  const bool async = a.D % 4 == 0 && reinterpret_cast<uintptr_t>(a.q) % 16 == 0 && reinterpret_cast<uintptr_t>(a.k) % 16 == 0 &&
+                     reinterpret_cast<uintptr_t>(a.state) % 16 == 0 && a.slot_stride % 4 == 0;
+  auto kernel = async ? delta_scan_kernel<T, KPL, L, true> : delta_scan_kernel<T, KPL, L, false>;
   if (smem > 48 * 1024 &&
       cuda_failed(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem))))
     return ERR_CUDA;
-  kernel<<<dim3(rows, a.heads, (a.V + cols - 1) / cols), DS_THREADS, smem, s>>>(a, L);
+  kernel<<<dim3(rows, a.heads, (a.V + cols - 1) / cols), DS_THREADS, smem, s>>>(a);
   return launch_result();
+}
+
+template <typename T>
+static int delta_scan_dispatch(const DeltaScanArgs& a, int rows, cudaStream_t s) {
+  // Channels a lane holds and lanes a column: a column spreads over 4 lanes up to 64 channels (two rounds of
+  // exchanges a token), over 8 up to 128, 16 up to 256, a whole warp beyond.
+  const int D = a.D;
+  if (D <= 16) return delta_scan_launch<T, 4, 4>(a, rows, s);
+  if (D <= 32) return delta_scan_launch<T, 8, 4>(a, rows, s);
+  if (D <= 64) return delta_scan_launch<T, 16, 4>(a, rows, s);
+  if (D <= 128) return delta_scan_launch<T, 16, 8>(a, rows, s);
+  if (D <= 256) return delta_scan_launch<T, 16, 16>(a, rows, s);
+  return delta_scan_launch<T, 16, 32>(a, rows, s);
 }
 
 ZB_API int zb_delta_scan(float* out, const float* q, const float* k, const void* v, long long v_stride,
@@ -229,13 +336,5 @@ ZB_API int zb_delta_scan(float* out, const float* q, const float* k, const void*
   a.heads = heads; a.heads_per_group = heads_per_group; a.D = D; a.V = V; a.num_slots = num_slots;
   a.write_state = write_state; a.status = status;
   auto s = static_cast<cudaStream_t>(stream);
-  // Few channels: 4 a lane, so that a column still spreads over several lanes; many: 16 a lane.
-  const int kpl = D <= 64 ? 4 : 16;
-  int L = 1;
-  while (L * kpl < D) L *= 2;
-  if (L > 32) return ERR_UNSUPPORTED;
-  if (dtype == DTYPE_F32)
-    return kpl == 4 ? delta_scan_launch<float, 4>(a, L, rows, s) : delta_scan_launch<float, 16>(a, L, rows, s);
-  return kpl == 4 ? delta_scan_launch<__nv_bfloat16, 4>(a, L, rows, s)
-                  : delta_scan_launch<__nv_bfloat16, 16>(a, L, rows, s);
+  return dtype == DTYPE_F32 ? delta_scan_dispatch<float>(a, rows, s) : delta_scan_dispatch<__nv_bfloat16>(a, rows, s);
 }

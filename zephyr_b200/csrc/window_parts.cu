@@ -150,8 +150,11 @@ struct PoolBlocksArgs {
   int* status;
 };
 
+constexpr int POOL_PAGES_KEPT = 256;     // a block's pages are looked up once, up to this many positions
+
 template <typename T>
 __global__ void __launch_bounds__(128) pool_blocks_kernel(const PoolBlocksArgs a) {
+  __shared__ int page_of[POOL_PAGES_KEPT];
   const int t = blockIdx.x;
   const int pos = a.positions[t];
   if ((pos + 1) % a.pool != 0) return;           // only the token that completes a block has work
@@ -167,12 +170,55 @@ __global__ void __launch_bounds__(128) pool_blocks_kernel(const PoolBlocksArgs a
     if (threadIdx.x == 0) report(a.status, STATUS_PAGE_OUT_OF_RANGE, out_page, t);
     return;
   }
+  auto lookup = [&](int p) {
+    const int block = p / a.page_size;
+    const int page = block < a.max_blocks ? a.block_table[static_cast<long long>(row) * a.max_blocks + block] : -1;
+    if (page <= 0 || page >= a.num_pages) {
+      report(a.status, STATUS_PAGE_OUT_OF_RANGE, page, t);
+      return 0;
+    }
+    return page;
+  };
+  for (int j = threadIdx.x; j < min(a.pool, POOL_PAGES_KEPT); j += blockDim.x) page_of[j] = lookup(b * a.pool + j);
+  __syncthreads();
   const long long page_elems = static_cast<long long>(a.nkv) * a.page_size * (a.kd + a.vd);
   const long long value_part = static_cast<long long>(a.nkv) * a.page_size * a.kd;
   const T* cache = static_cast<const T*>(a.cache);
   T* pooled = static_cast<T*>(a.pool_cache);
-  const int per_head = a.kd + a.vd;
   const float inv = 1.0f / static_cast<float>(a.pool);
+  constexpr int vec = 16 / static_cast<int>(sizeof(T));
+  if (a.kd % vec == 0 && a.vd % vec == 0) {
+    // Rows of whole 16-byte pieces: a thread owns one piece of one head's key or value and walks the block.
+    const int k_pieces = a.kd / vec, v_pieces = a.vd / vec, per_head = k_pieces + v_pieces;
+    for (int e = threadIdx.x; e < a.nkv * per_head; e += blockDim.x) {
+      const int kvh = e / per_head, c = e - kvh * per_head;
+      const bool is_v = c >= k_pieces;
+      const int dim = is_v ? a.vd : a.kd, pieces = is_v ? v_pieces : k_pieces, piece = is_v ? c - k_pieces : c;
+      float sum[vec];
+#pragma unroll
+      for (int u = 0; u < vec; ++u) sum[u] = 0.0f;
+      for (int j = 0; j < a.pool; ++j) {
+        const int p = b * a.pool + j;
+        const int page = j < POOL_PAGES_KEPT ? page_of[j] : lookup(p);
+        if (page == 0) continue;
+        const long long base = static_cast<long long>(page) * page_elems + (is_v ? value_part : 0) +
+                               (static_cast<long long>(kvh) * a.page_size + p % a.page_size) * dim;
+        const uint4 raw = *reinterpret_cast<const uint4*>(cache + base + (piece ^ kv_swizzle(p, pieces)) * vec);
+        const T* values = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+        for (int u = 0; u < vec; ++u) sum[u] += to_float(values[u]);
+      }
+      uint4 raw;
+      T* values = reinterpret_cast<T*>(&raw);
+#pragma unroll
+      for (int u = 0; u < vec; ++u) values[u] = from_float<T>(sum[u] * inv);
+      const long long base = static_cast<long long>(out_page) * page_elems + (is_v ? value_part : 0) +
+                             (static_cast<long long>(kvh) * a.page_size + b % a.page_size) * dim;
+      *reinterpret_cast<uint4*>(pooled + base + (piece ^ kv_swizzle(b, pieces)) * vec) = raw;
+    }
+    return;
+  }
+  const int per_head = a.kd + a.vd;
   for (int e = threadIdx.x; e < a.nkv * per_head; e += blockDim.x) {
     const int kvh = e / per_head, c = e - kvh * per_head;
     const bool is_v = c >= a.kd;
@@ -180,12 +226,9 @@ __global__ void __launch_bounds__(128) pool_blocks_kernel(const PoolBlocksArgs a
     const bool permuted = (dim * static_cast<int>(sizeof(T))) % 16 == 0;
     float sum = 0.0f;
     for (int j = 0; j < a.pool; ++j) {
-      const int p = b * a.pool + j, block = p / a.page_size;
-      const int page = block < a.max_blocks ? a.block_table[static_cast<long long>(row) * a.max_blocks + block] : -1;
-      if (page <= 0 || page >= a.num_pages) {
-        report(a.status, STATUS_PAGE_OUT_OF_RANGE, page, t);
-        continue;
-      }
+      const int p = b * a.pool + j;
+      const int page = j < POOL_PAGES_KEPT ? page_of[j] : lookup(p);
+      if (page == 0) continue;
       const long long base = static_cast<long long>(page) * page_elems + (is_v ? value_part : 0) +
                              (static_cast<long long>(kvh) * a.page_size + p % a.page_size) * dim;
       sum += to_float(cache[base + (permuted ? kv_element_index(i, p, dim, sizeof(T)) : i)]);
