@@ -75,8 +75,9 @@ def _run_attention(cuda_device, dtype, q, k, v, H, G, page, portions, *, window,
             wide_q0 = torch.arange(0, n, ops.paged_prefill_tile_tokens(), dtype=torch.int32, device=cuda_device)
             out = torch.full((n, H * dv * (G if mix is not None else 1)), float("nan"), device=cuda_device,
                              dtype=torch.float32 if mix is not None else torch_dtype)
+            # (a single token's query rows are the heads of a group)
             ops.paged_prefill(qs, cache, table, torch.zeros_like(wide_q0), wide_q0, *rows, H, G, d, window, scale, status, out,
-                              keep_first=keep_first, cross_values=mix is not None, **extra)
+                              keep_first=keep_first, cross_values=mix is not None, by_group=n == 1, **extra)
             outs.append(ops.head_mix(out, mix.float().to(cuda_device), H, G, dv, torch_dtype) if mix is not None else out)
         elif mix is not None:
             crossed = ops.paged_attention(*args, value_dim=dv, keep_first=keep_first, cross_values=True,

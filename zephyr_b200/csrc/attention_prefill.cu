@@ -20,6 +20,11 @@
 // the result being [T, nh, nkv, hd] (what a mixing of the heads' weights behind the softmax is a linear map
 // of); `out_f32` writes the result unrounded.
 //
+// `by_group` (template DEC): a tile is ONE new token of a request and the CTA's query rows are the heads that
+// share a key/value head (row r = head kvh * g + r, all at the token's position), so a decoded token's keys
+// and values stream once for the whole group and the products fill the tensor cores' rows with heads; the
+// grid's x counts key/value heads (times value heads with `cross_values`).
+//
 // Head sizes: every multiple of 32 up to 256 (a query tile's outputs stay in registers: 16 float32
 // values a thread for every 32 of the head).  A tile may hold a single token (one warp works, the
 // others help to fetch): latent attention serves decoded tokens this way where the split-context
@@ -61,7 +66,7 @@ struct PrefillArgs {
   int* status;
 };
 
-template <int HD>
+template <int HD, bool DEC>
 __global__ void __launch_bounds__(PRE_WARPS * 32, 1)
 paged_prefill_kernel(const PrefillArgs a) {
   static_assert(HD % 32 == 0 && HD <= 256, "head sizes that are multiples of 32, up to 256");
@@ -75,17 +80,20 @@ paged_prefill_kernel(const PrefillArgs a) {
   // The host lists the tiles by the number of keys they see, fewest first: take the list back to
   // front, and all heads of a tile before the next tile, so that the longest work of the whole
   // launch starts first and the short tiles fill the gaps at the end.
-  const int tile = gridDim.y - 1 - blockIdx.y, head = blockIdx.x % a.nh;
+  const int tile = gridDim.y - 1 - blockIdx.y;
+  const int across = DEC ? a.nkv : a.nh;           // what the grid's x counts: key/value heads, or query heads
+  const int head = DEC ? (blockIdx.x % across) * (a.nh / a.nkv) : blockIdx.x % across;   // (DEC: the group's first head)
   const int row = a.tile_row[tile], q0 = a.tile_q0[tile];
   if (row < 0 || row >= a.num_rows) {
     if (threadIdx.x == 0) report(a.status, STATUS_ROW_OUT_OF_RANGE, row, tile);
     return;
   }
   const int g = a.nh / a.nkv, kvh = head / g;
-  const int vh = a.cross_values ? blockIdx.x / a.nh : kvh;        // whose values
+  const int vh = a.cross_values ? blockIdx.x / across : kvh;      // whose values
   const int q_len = a.row_q_len[row], ctx = a.row_ctx[row], tok0 = a.row_q_start[row] + q0;
-  const int n_tok = min(PRE_BM, q_len - q0);
+  const int n_tok = DEC ? min(1, q_len - q0) : min(PRE_BM, q_len - q0);
   if (n_tok <= 0) return;
+  const int n_rows = DEC ? min(g, PRE_BM) : n_tok;       // query rows of this CTA: heads of the group, or tokens
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int quad_row = lane >> 2, quad_col = (lane & 3) * 2;
   const int* table = a.block_table + static_cast<size_t>(row) * a.max_blocks;
@@ -105,8 +113,10 @@ paged_prefill_kernel(const PrefillArgs a) {
 
   for (int e = threadIdx.x; e < PRE_BM * CHUNKS; e += PRE_WARPS * 32) {
     const int j = e / CHUNKS, c = (e - j * CHUNKS) * 8;
-    const bool ok = j < n_tok;
-    cp_async_16(q_s + j * KROW + c, a.q + (static_cast<size_t>(tok0 + (ok ? j : 0)) * a.nh + head) * HD + c, ok);
+    const bool ok = j < n_rows;
+    const size_t from = DEC ? static_cast<size_t>(tok0) * a.nh + head + (ok ? j : 0)
+                            : static_cast<size_t>(tok0 + (ok ? j : 0)) * a.nh + head;
+    cp_async_16(q_s + j * KROW + c, a.q + from * HD + c, ok);
   }
   auto load_tile = [&](int t) {
     __nv_bfloat16* ks = ring + (t & 1) * STAGE;
@@ -148,11 +158,12 @@ paged_prefill_kernel(const PrefillArgs a) {
 
   // This warp's 16 query rows; this lane's two rows sit at positions qpos[0] and qpos[1].
   const int warp_row0 = warp * 16;
-  const bool warp_active = warp_row0 < n_tok;
-  const int qpos[2] = {ctx + q0 + warp_row0 + quad_row, ctx + q0 + warp_row0 + quad_row + 8};
-  const int warp_last_pos = ctx + q0 + min(warp_row0 + 15, n_tok - 1);
-  int warp_first_visible = a.window > 0 ? max(0, ctx + q0 + warp_row0 - a.window + 1) : 0;
-  if (a.chunk > 0) warp_first_visible = max(warp_first_visible, (ctx + q0 + warp_row0) / a.chunk * a.chunk);
+  const bool warp_active = warp_row0 < n_rows;
+  const int warp_pos0 = DEC ? ctx + q0 : ctx + q0 + warp_row0;      // the position of the warp's first row
+  const int qpos[2] = {DEC ? warp_pos0 : warp_pos0 + quad_row, DEC ? warp_pos0 : warp_pos0 + quad_row + 8};
+  const int warp_last_pos = DEC ? warp_pos0 : ctx + q0 + min(warp_row0 + 15, n_tok - 1);
+  int warp_first_visible = a.window > 0 ? max(0, warp_pos0 - a.window + 1) : 0;
+  if (a.chunk > 0) warp_first_visible = max(warp_first_visible, warp_pos0 / a.chunk * a.chunk);
   const int chunk_start[2] = {a.chunk > 0 ? qpos[0] / a.chunk * a.chunk : 0, a.chunk > 0 ? qpos[1] / a.chunk * a.chunk : 0};
 
   unsigned qa[HD / 16][4];
@@ -262,13 +273,15 @@ paged_prefill_kernel(const PrefillArgs a) {
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int r = warp_row0 + quad_row + 8 * h;
-    if (r >= n_tok) continue;
+    if (r >= n_rows) continue;
+    const int row_head = DEC ? head + r : head;
+    const size_t row_token = DEC ? tok0 : tok0 + r;
     float denominator = l_run[h];
     if (a.sinks != nullptr)      // one more exponential, relative to the running maximum (both in powers of two)
-      denominator += exp2f(a.sinks[head] * 1.4426950408889634f - m_run[h]);
+      denominator += exp2f(a.sinks[row_head] * 1.4426950408889634f - m_run[h]);
     const float inv = denominator > 0.0f ? 1.0f / denominator : 0.0f;
-    const size_t at = (a.cross_values ? (static_cast<size_t>(tok0 + r) * a.nh + head) * a.nkv + vh
-                                      : static_cast<size_t>(tok0 + r) * a.nh + head) * HD + quad_col;
+    const size_t at = (a.cross_values ? (row_token * a.nh + row_head) * a.nkv + vh
+                                      : row_token * a.nh + row_head) * HD + quad_col;
     if (a.out_f32) {
       float* dst = reinterpret_cast<float*>(a.out) + at;
 #pragma unroll
@@ -284,12 +297,13 @@ paged_prefill_kernel(const PrefillArgs a) {
 }
 
 template <int HD>
-int prefill_launch(const PrefillArgs& a, int n_tiles, cudaStream_t stream) {
+int prefill_launch(const PrefillArgs& a, int n_tiles, cudaStream_t stream, bool by_group = false) {
   const size_t smem = (static_cast<size_t>(PRE_BM) + 4 * PRE_BN) * (HD + 8) * sizeof(__nv_bfloat16);
-  auto kernel = paged_prefill_kernel<HD>;
+  auto kernel = by_group ? paged_prefill_kernel<HD, true> : paged_prefill_kernel<HD, false>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
     return ERR_CUDA;
-  kernel<<<dim3(a.cross_values ? a.nh * a.nkv : a.nh, n_tiles), PRE_WARPS * 32, smem, stream>>>(a);
+  const int across = by_group ? a.nkv : a.nh;
+  kernel<<<dim3(a.cross_values ? across * a.nkv : across, n_tiles), PRE_WARPS * 32, smem, stream>>>(a);
   return launch_result();
 }
 
@@ -314,10 +328,11 @@ ZB_API int zb_paged_prefill_windowed(void* out, const void* q, const void* kv_ca
                                      const int* row_ctx, int nh, int nkv, int hd, int window, int chunk, float scale,
                                      float softcap, int keys_only, const float* sinks, int keep_first, int pool,
                                      const void* pool_cache, const int* pool_table, int pool_max_blocks,
-                                     int pool_num_pages, int cross_values, int out_f32, int* status, void* stream) {
+                                     int pool_num_pages, int cross_values, int out_f32, int by_group, int* status,
+                                     void* stream) {
   if (n_tiles < 0 || page_size <= 0 || window < 0 || chunk < 0 || softcap < 0.0f || keep_first < 0 || pool < 0 ||
       (pool > 0 && (window <= 0 || pool_cache == nullptr || pool_table == nullptr || pool_max_blocks <= 0 || keys_only)) ||
-      (cross_values && keys_only) || nh * (cross_values ? nkv : 1) > 65535)
+      (cross_values && keys_only) || nh * (cross_values ? nkv : 1) > 65535 || (by_group && nh / (nkv > 0 ? nkv : 1) > PRE_BM))
     return ERR_BAD_ARGUMENT;
   if (!zb_paged_prefill_supported(nh, nkv, hd, DTYPE_BF16)) return ERR_UNSUPPORTED;
   if (n_tiles == 0) return OK;
@@ -341,14 +356,14 @@ ZB_API int zb_paged_prefill_windowed(void* out, const void* q, const void* kv_ca
   a.status = status;
   auto s = static_cast<cudaStream_t>(stream);
   switch (hd) {
-    case 32: return prefill_launch<32>(a, n_tiles, s);
-    case 64: return prefill_launch<64>(a, n_tiles, s);
-    case 96: return prefill_launch<96>(a, n_tiles, s);
-    case 128: return prefill_launch<128>(a, n_tiles, s);
-    case 160: return prefill_launch<160>(a, n_tiles, s);
-    case 192: return prefill_launch<192>(a, n_tiles, s);
-    case 224: return prefill_launch<224>(a, n_tiles, s);
-    default: return prefill_launch<256>(a, n_tiles, s);
+    case 32: return prefill_launch<32>(a, n_tiles, s, by_group != 0);
+    case 64: return prefill_launch<64>(a, n_tiles, s, by_group != 0);
+    case 96: return prefill_launch<96>(a, n_tiles, s, by_group != 0);
+    case 128: return prefill_launch<128>(a, n_tiles, s, by_group != 0);
+    case 160: return prefill_launch<160>(a, n_tiles, s, by_group != 0);
+    case 192: return prefill_launch<192>(a, n_tiles, s, by_group != 0);
+    case 224: return prefill_launch<224>(a, n_tiles, s, by_group != 0);
+    default: return prefill_launch<256>(a, n_tiles, s, by_group != 0);
   }
 }
 
@@ -359,7 +374,7 @@ ZB_API int zb_paged_prefill_masked(void* out, const void* q, const void* kv_cach
                                    float softcap, int keys_only, const float* sinks, int* status, void* stream) {
   return zb_paged_prefill_windowed(out, q, kv_cache, block_table, max_blocks, page_size, num_pages, num_rows, tile_row,
                                    tile_q0, n_tiles, row_q_start, row_q_len, row_ctx, nh, nkv, hd, window, chunk, scale,
-                                   softcap, keys_only, sinks, 0, 0, nullptr, nullptr, 0, 0, 0, 0, status, stream);
+                                   softcap, keys_only, sinks, 0, 0, nullptr, nullptr, 0, 0, 0, 0, 0, status, stream);
 }
 
 ZB_API int zb_paged_prefill(void* out, const void* q, const void* kv_cache, const int* block_table, int max_blocks,

@@ -147,7 +147,7 @@ _SIGNATURES = {
     "zb_paged_prefill_windowed": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                                   c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                                   c_float, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                  c_void_p, c_void_p],
+                                  c_int, c_void_p, c_void_p],
     "zb_paged_decode_fused": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p,
                               c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                               c_longlong, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_int, c_void_p],
@@ -1290,17 +1290,20 @@ def paged_prefill(q: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.Te
                   nh: int, nkv: int, hd: int, window: int, scale: float, status: torch.Tensor,
                   out: torch.Tensor, chunk: int = 0, sinks: torch.Tensor | None = None, softcap: float = 0.0,
                   keys_only: bool = False, keep_first: int = 0, pool: int = 0, pool_cache: torch.Tensor | None = None,
-                  pool_table: torch.Tensor | None = None, cross_values: bool = False) -> torch.Tensor:
+                  pool_table: torch.Tensor | None = None, cross_values: bool = False,
+                  by_group: bool = False) -> torch.Tensor:
     """Tensor-core attention for rows with several new tokens, cut into tiles of
     ``paged_prefill_tile_tokens()``; writes those tokens' rows of ``out``.  ``chunk``, ``sinks`` and
     ``softcap`` as in ``paged_attention``, ``keys_only`` as its ``shared_kv``.  Head size 128 runs on tcgen05
     with the accumulators in tensor memory (every form but the chunked mask), other sizes and chunked masks
     on mma.sync.  ``keep_first``, ``pool`` with its store, and ``cross_values`` (``out`` is then
-    [T, nh * nkv * hd], bfloat16 or float32) as in ``paged_attention``: these run on mma.sync."""
+    [T, nh * nkv * hd], bfloat16 or float32) as in ``paged_attention``: these run on mma.sync.  ``by_group``: every
+    tile is one new token (the tiles of single-token rows), and a CTA's query rows are the heads that share a
+    key/value head: a decoded token's keys and values stream once a group."""
     _cuda(q, kv_cache, block_table, tile_row, tile_q0, row_q_start, row_q_len, row_ctx, status, out, pool_cache, pool_table)
     _i32(block_table, tile_row, tile_q0, row_q_start, row_q_len, row_ctx)
     _require(q.dim() == 2 and q.is_contiguous() and q.shape[1] == nh * hd and q.dtype == torch.bfloat16, "q shape")
-    windowed = bool(keep_first or pool or cross_values)
+    windowed = bool(keep_first or pool or cross_values or by_group)
     if windowed:
         _require(out.shape == (q.shape[0], nh * hd * (nkv if cross_values else 1)) and out.is_contiguous()
                  and out.dtype in ((torch.float32, q.dtype) if cross_values else (q.dtype,)), "out: [T, nh (* nkv) * hd]")
@@ -1329,7 +1332,8 @@ def paged_prefill(q: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.Te
         _check(library().zb_paged_prefill_windowed(*common, int(chunk), float(scale), float(softcap), int(keys_only),
                                                    _ptr(sinks), int(keep_first), int(pool), _ptr(pool_cache),
                                                    _ptr(pool_table), pool_blocks, pool_pages, int(cross_values),
-                                                   int(out.dtype == torch.float32), _ptr(status), _stream()), "paged_prefill")
+                                                   int(out.dtype == torch.float32), int(by_group), _ptr(status),
+                                                   _stream()), "paged_prefill")
     else:
         _check(library().zb_paged_prefill_masked(*common, int(chunk), float(scale), float(softcap), int(keys_only),
                                                  _ptr(sinks), _ptr(status), _stream()), "paged_prefill")

@@ -308,7 +308,8 @@ class Attention(Mixer):
     def _attend_windowed(self, q: torch.Tensor, ctx: StepContext, call: LayerCall, cache, table) -> torch.Tensor:
         """Attention with kept first tokens, pooled blocks or mixed heads: every row, prompts and single
         tokens alike, on the mma.sync prompt kernel where it takes the shape (bfloat16, one width for keys
-        and values that is a multiple of 32 up to 256), on the general kernel elsewhere.  With mixed heads
+        and values that is a multiple of 32 up to 256; a single token's query rows are the heads of a group, so
+        its keys and values stream once a group), on the general kernel elsewhere.  With mixed heads
         the kernel hands out every head's weights on every key/value head's values, unrounded, and a second
         kernel mixes them."""
         masks = {"chunk": self.chunk, "sinks": self.sinks, "keep_first": self.keep_first}
@@ -322,9 +323,12 @@ class Attention(Mixer):
         out = torch.empty((q.shape[0], width), dtype=torch.float32 if mixed else q.dtype, device=q.device)
         common = (self.nh, self.nkv, self.hd, self.window, self.scale, ctx.status)
         if self.fast_prefill:
-            tile_row, tile_q0 = ctx.tiles[(self.prefill_tile_tokens, "all")]
-            ops.paged_prefill(q, cache, table, tile_row, tile_q0, ctx.row_q_start, ctx.row_q_len, ctx.row_ctx, *common,
-                              out=out, cross_values=mixed, **masks)
+            # Rows with several tokens as tiles of tokens; single tokens as tiles of the heads of a group.
+            for which, by_group in ((self.prefill_tile_tokens, "multi"), False), ((self.tile_tokens, "single"), True):
+                tile_row, tile_q0 = ctx.tiles[which]
+                if tile_row.numel() > 0:
+                    ops.paged_prefill(q, cache, table, tile_row, tile_q0, ctx.row_q_start, ctx.row_q_len, ctx.row_ctx,
+                                      *common, out=out, cross_values=mixed, by_group=by_group, **masks)
         else:
             tile_row, tile_q0 = ctx.tiles[(self.tile_tokens, "all")]
             ops.paged_attention(q, cache, table, tile_row, tile_q0, self.tile_tokens, ctx.row_q_start, ctx.row_q_len,
