@@ -49,6 +49,7 @@ struct PrefillArgs {
   const int* row_q_len;          // [R]
   const int* row_ctx;            // [R]
   int max_blocks, page_size, num_pages, num_rows;
+  int page_shift;                // page_size = 1 << page_shift, or -1 where it is no power of two
   int nh, nkv, window;
   int chunk;                     // n > 0: a query at position p sees only keys >= (p / n) * n
   const float* sinks;            // null, or [nh]: exp(sinks[h]) joins the softmax's denominator of head h
@@ -138,7 +139,9 @@ paged_prefill_kernel(const PrefillArgs a) {
       const __nv_bfloat16* src = source;
       const __nv_bfloat16* vsrc = source;
       if (ok) {
-        const int block = pos / a.page_size;
+        // (a division by a size only known at run time costs tens of instructions, here for every 16 bytes)
+        const int block = a.page_shift >= 0 ? pos >> a.page_shift : pos / a.page_size;
+        const int in_page = a.page_shift >= 0 ? pos & (a.page_size - 1) : pos % a.page_size;
         const int page = block < max_blocks ? pages[block] : -1;
         if (page <= 0 || page >= num_pages) {
           report(a.status, STATUS_PAGE_OUT_OF_RANGE, page, tok0);
@@ -147,8 +150,8 @@ paged_prefill_kernel(const PrefillArgs a) {
           // logical chunk c / 8 of the row sits at the permuted chunk (common.cuh: kv_swizzle)
           const long long in_row = ((c >> 3) ^ kv_swizzle(pos, CHUNKS)) << 3;
           const long long page_heads = static_cast<long long>(page) * (a.keys_only ? 1 : 2) * a.nkv;
-          src += ((page_heads + kvh) * a.page_size + pos % a.page_size) * HD + in_row;
-          vsrc += ((page_heads + (a.keys_only ? kvh : a.nkv + vh)) * a.page_size + pos % a.page_size) * HD + in_row;
+          src += ((page_heads + kvh) * a.page_size + in_page) * HD + in_row;
+          vsrc += ((page_heads + (a.keys_only ? kvh : a.nkv + vh)) * a.page_size + in_page) * HD + in_row;
         }
       }
       cp_async_16(ks + j * KROW + c, src, ok);
@@ -162,7 +165,7 @@ paged_prefill_kernel(const PrefillArgs a) {
   }
 
   // This warp's 16 query rows; this lane's two rows sit at positions qpos[0] and qpos[1].
-  const int warp_row0 = warp * 16;
+  const int warp_row0 = DEC ? 0 : warp * 16;
   const bool warp_active = warp_row0 < n_rows;
   const int warp_pos0 = DEC ? ctx + q0 : ctx + q0 + warp_row0;      // the position of the warp's first row
   const int qpos[2] = {DEC ? warp_pos0 : warp_pos0 + quad_row, DEC ? warp_pos0 : warp_pos0 + quad_row + 8};
@@ -170,6 +173,9 @@ paged_prefill_kernel(const PrefillArgs a) {
   int warp_first_visible = a.window > 0 ? max(0, warp_pos0 - a.window + 1) : 0;
   if (a.chunk > 0) warp_first_visible = max(warp_first_visible, warp_pos0 / a.chunk * a.chunk);
   const int chunk_start[2] = {a.chunk > 0 ? qpos[0] / a.chunk * a.chunk : 0, a.chunk > 0 ? qpos[1] / a.chunk * a.chunk : 0};
+  // Pooled entries in sight of this lane's two rows, and of the warp's last row: worked out once, not per score.
+  const int seen[2] = {a.pool > 0 ? (qpos[0] - a.window + 1) / a.pool : 0, a.pool > 0 ? (qpos[1] - a.window + 1) / a.pool : 0};
+  const int warp_seen = a.pool > 0 ? (warp_last_pos - a.window + 1) / a.pool : 0;
 
   unsigned qa[HD / 16][4];
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
@@ -191,40 +197,44 @@ paged_prefill_kernel(const PrefillArgs a) {
     const int k0 = run == 0 ? t * PRE_BN : (run == 1 ? (t - pool_tiles) * PRE_BN
                                                      : first_tile + (t - pool_tiles - kept_tiles) * PRE_BN);
     if (!warp_active) continue;                          // uniform over the warp, as are the next two
-    if (run == 0 && k0 >= (warp_last_pos - a.window + 1) / a.pool) continue;
+    if (run == 0 && k0 >= warp_seen) continue;
     if (run == 2 && (k0 > warp_last_pos || (k0 + PRE_BN <= warp_first_visible && k0 >= a.keep_first))) continue;
     const __nv_bfloat16* ks_tile = ring + (t % NS) * STAGE;
     const __nv_bfloat16* vs_tile = ks_tile + PRE_BN * KROW;
 
-    float s[PRE_BN / 8][4];
+    // The key tiles of 8 this warp works on: all eight of the 64 keys, or (DEC) the warp's own one.
+    constexpr int NTS = DEC ? 1 : PRE_BN / 8;
+    float s[NTS][4];
 #pragma unroll
-    for (int nt = 0; nt < PRE_BN / 8; ++nt) {
-      s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f;
+    for (int i = 0; i < NTS; ++i) {
+      const int nt = DEC ? warp : i;
+      s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
 #pragma unroll
       for (int kk = 0; kk < HD / 32; ++kk) {
         unsigned b[4];
         ldmatrix_x4(b, ks_tile + (nt * 8 + (lane & 7)) * KROW + kk * 32 + (lane >> 3) * 8);
-        mma_bf16_16816(s[nt], qa[2 * kk], b[0], b[1]);
-        mma_bf16_16816(s[nt], qa[2 * kk + 1], b[2], b[3]);
+        mma_bf16_16816(s[i], qa[2 * kk], b[0], b[1]);
+        mma_bf16_16816(s[i], qa[2 * kk + 1], b[2], b[3]);
       }
     }
 
     float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-    for (int nt = 0; nt < PRE_BN / 8; ++nt) {
+    for (int i = 0; i < NTS; ++i) {
+      const int nt = DEC ? warp : i;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         const int pos = k0 + nt * 8 + quad_col + (c & 1);
         const int qp = qpos[c >> 1];
-        const bool valid = run == 0 ? pos < (qp - a.window + 1) / a.pool
+        const bool valid = run == 0 ? pos < seen[c >> 1]
                          : run == 1 ? pos < kept
                                     : pos <= qp && pos >= lo &&
                                           (a.window == 0 || pos > qp - a.window || pos < a.keep_first) &&
                                           pos >= chunk_start[c >> 1];
-        const float scaled = a.softcap_log2 > 0.0f ? a.softcap_log2 * tanhf(s[nt][c] * a.scale_over_cap)
-                                                   : s[nt][c] * a.scale_log2;
-        s[nt][c] = valid ? scaled : -INFINITY;
-        tile_max[c >> 1] = fmaxf(tile_max[c >> 1], s[nt][c]);
+        const float scaled = a.softcap_log2 > 0.0f ? a.softcap_log2 * tanhf(s[i][c] * a.scale_over_cap)
+                                                   : s[i][c] * a.scale_log2;
+        s[i][c] = valid ? scaled : -INFINITY;
+        tile_max[c >> 1] = fmaxf(tile_max[c >> 1], s[i][c]);
       }
     }
     float corr[2], m_use[2];
@@ -239,11 +249,11 @@ paged_prefill_kernel(const PrefillArgs a) {
     }
     float row_sum[2] = {0.0f, 0.0f};
 #pragma unroll
-    for (int nt = 0; nt < PRE_BN / 8; ++nt) {
+    for (int i = 0; i < NTS; ++i) {
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        s[nt][c] = exp2f(s[nt][c] - m_use[c >> 1]);
-        row_sum[c >> 1] += s[nt][c];
+        s[i][c] = exp2f(s[i][c] - m_use[c >> 1]);
+        row_sum[c >> 1] += s[i][c];
       }
     }
 #pragma unroll
@@ -256,24 +266,77 @@ paged_prefill_kernel(const PrefillArgs a) {
     for (int n = 0; n < HD / 8; ++n) {
       o[n][0] *= corr[0]; o[n][1] *= corr[0]; o[n][2] *= corr[1]; o[n][3] *= corr[1];
     }
-#pragma unroll
-    for (int ks = 0; ks < PRE_BN / 16; ++ks) {
-      unsigned pa[4];
-      pa[0] = pack_bf16(s[2 * ks][0], s[2 * ks][1]);
-      pa[1] = pack_bf16(s[2 * ks][2], s[2 * ks][3]);
-      pa[2] = pack_bf16(s[2 * ks + 1][0], s[2 * ks + 1][1]);
-      pa[3] = pack_bf16(s[2 * ks + 1][2], s[2 * ks + 1][3]);
+    if (DEC) {
+      // 8 keys: the product's second half of 8 takes zero weights (and reads the same 8 value rows again).
+      unsigned pa[4] = {pack_bf16(s[0][0], s[0][1]), pack_bf16(s[0][2], s[0][3]), 0u, 0u};
 #pragma unroll
       for (int n2 = 0; n2 < HD / 16; ++n2) {
         unsigned b[4];
-        ldmatrix_x4_trans(b, vs_tile + (ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * KROW + n2 * 16 + (lane >> 4) * 8);
+        ldmatrix_x4_trans(b, vs_tile + (warp * 8 + (lane & 7)) * KROW + n2 * 16 + (lane >> 4) * 8);
         mma_bf16_16816(o[2 * n2], pa, b[0], b[1]);
         mma_bf16_16816(o[2 * n2 + 1], pa, b[2], b[3]);
+      }
+    } else {
+#pragma unroll
+      for (int ks = 0; ks < NTS / 2; ++ks) {
+        unsigned pa[4];
+        pa[0] = pack_bf16(s[2 * ks][0], s[2 * ks][1]);
+        pa[1] = pack_bf16(s[2 * ks][2], s[2 * ks][3]);
+        pa[2] = pack_bf16(s[(2 * ks + 1) % NTS][0], s[(2 * ks + 1) % NTS][1]);
+        pa[3] = pack_bf16(s[(2 * ks + 1) % NTS][2], s[(2 * ks + 1) % NTS][3]);
+#pragma unroll
+        for (int n2 = 0; n2 < HD / 16; ++n2) {
+          unsigned b[4];
+          ldmatrix_x4_trans(b, vs_tile + (ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * KROW + n2 * 16 + (lane >> 4) * 8);
+          mma_bf16_16816(o[2 * n2], pa, b[0], b[1]);
+          mma_bf16_16816(o[2 * n2 + 1], pa, b[2], b[3]);
+        }
       }
     }
   }
   cp_async_wait<0>();
 
+  if (DEC) {
+    // The eight warps' partial results meet in shared memory (the ring is no longer read): each row's
+    // maxima and sums, and its outputs, then 256 threads share the rows' values.
+    __syncthreads();
+    float* part_o = reinterpret_cast<float*>(ring);                 // [warps][16][HD]
+    float* part_m = reinterpret_cast<float*>(q_s);                  // [warps][16], then the sums
+    float* part_l = part_m + PRE_WARPS * 16;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int r = quad_row + 8 * h;
+      if ((lane & 3) == 0) {
+        part_m[warp * 16 + r] = m_run[h];
+        part_l[warp * 16 + r] = l_run[h];
+      }
+#pragma unroll
+      for (int n = 0; n < HD / 8; ++n)
+        *reinterpret_cast<float2*>(part_o + (warp * 16 + r) * HD + n * 8 + quad_col) = make_float2(o[n][2 * h], o[n][2 * h + 1]);
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < n_rows * HD; e += PRE_WARPS * 32) {
+      const int r = e / HD, d = e - r * HD;
+      float top = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < PRE_WARPS; ++w) top = fmaxf(top, part_m[w * 16 + r]);
+      float denominator = 0.0f, value = 0.0f;
+#pragma unroll
+      for (int w = 0; w < PRE_WARPS; ++w) {
+        const float weight = top == -INFINITY ? 0.0f : exp2f(part_m[w * 16 + r] - top);
+        denominator = fmaf(part_l[w * 16 + r], weight, denominator);
+        value = fmaf(part_o[(w * 16 + r) * HD + d], weight, value);
+      }
+      const int row_head = head + r;
+      if (a.sinks != nullptr) denominator += exp2f(a.sinks[row_head] * 1.4426950408889634f - top);
+      const float result = denominator > 0.0f ? value / denominator : 0.0f;
+      const size_t at = (a.cross_values ? (static_cast<size_t>(tok0) * a.nh + row_head) * a.nkv + vh
+                                        : static_cast<size_t>(tok0) * a.nh + row_head) * HD + d;
+      if (a.out_f32) reinterpret_cast<float*>(a.out)[at] = result;
+      else a.out[at] = __float2bfloat16_rn(result);
+    }
+    return;
+  }
   if (!warp_active) return;
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
@@ -339,7 +402,7 @@ ZB_API int zb_paged_prefill_windowed(void* out, const void* q, const void* kv_ca
                                      void* stream) {
   if (n_tiles < 0 || page_size <= 0 || window < 0 || chunk < 0 || softcap < 0.0f || keep_first < 0 || pool < 0 ||
       (pool > 0 && (window <= 0 || pool_cache == nullptr || pool_table == nullptr || pool_max_blocks <= 0 || keys_only)) ||
-      (cross_values && keys_only) || nh * (cross_values ? nkv : 1) > 65535 || (by_group && nh / (nkv > 0 ? nkv : 1) > PRE_BM))
+      (cross_values && keys_only) || nh * (cross_values ? nkv : 1) > 65535 || (by_group && nh / (nkv > 0 ? nkv : 1) > 16))
     return ERR_BAD_ARGUMENT;
   if (!zb_paged_prefill_supported(nh, nkv, hd, DTYPE_BF16)) return ERR_UNSUPPORTED;
   if (n_tiles == 0) return OK;
@@ -351,6 +414,9 @@ ZB_API int zb_paged_prefill_windowed(void* out, const void* q, const void* kv_ca
   a.block_table = block_table; a.tile_row = tile_row; a.tile_q0 = tile_q0;
   a.row_q_start = row_q_start; a.row_q_len = row_q_len; a.row_ctx = row_ctx;
   a.max_blocks = max_blocks; a.page_size = page_size; a.num_pages = num_pages; a.num_rows = num_rows;
+  a.page_shift = -1;
+  for (int shift = 0; shift < 31; ++shift)
+    if (page_size == (1 << shift)) a.page_shift = shift;
   a.nh = nh; a.nkv = nkv; a.window = window; a.chunk = chunk; a.sinks = sinks;
   a.scale_log2 = scale * 1.4426950408889634f;
   a.softcap_log2 = softcap * 1.4426950408889634f;

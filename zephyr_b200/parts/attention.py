@@ -324,7 +324,9 @@ class Attention(Mixer):
         common = (self.nh, self.nkv, self.hd, self.window, self.scale, ctx.status)
         if self.fast_prefill:
             # Rows with several tokens as tiles of tokens; single tokens as tiles of the heads of a group.
-            for which, by_group in ((self.prefill_tile_tokens, "multi"), False), ((self.tile_tokens, "single"), True):
+            # (The kernel takes groups of up to 16 heads that way; larger ones run as tiles of one token.)
+            for which, by_group in (((self.prefill_tile_tokens, "multi"), False),
+                                    ((self.tile_tokens, "single"), self.group <= 16)):
                 tile_row, tile_q0 = ctx.tiles[which]
                 if tile_row.numel() > 0:
                     ops.paged_prefill(q, cache, table, tile_row, tile_q0, ctx.row_q_start, ctx.row_q_len, ctx.row_ctx,

@@ -24,7 +24,7 @@ class RMSNorm(Norm):
         self.eps = float(spec.eps)
         self.dtype = dtype
         self.weight = weights[spec.weight]
-        self._scale32 = None        # the scales as float32, made when the fused residual form first asks
+        self._scale32 = self.weight.float().contiguous()     # what the fused residual form reads
 
     @staticmethod
     def weight_decls(spec: NormSpec) -> dict[str, WeightDecl]:
@@ -60,12 +60,8 @@ class RMSNorm(Norm):
         """residual (float32) += mult * norm(delta), in place and in one kernel; with ``then`` also returns
         then(residual), with ``rounded_sum`` the sum itself in delta's type: the form a block with norms
         behind its parts uses."""
-        if self._scale32 is None:
-            self._scale32 = self.weight.float().contiguous()
         if then is None:
             return ops.residual_rms_norm(residual, delta, self._scale32, self.eps, mult, rounded_sum=rounded_sum)
-        if then._scale32 is None:
-            then._scale32 = then.weight.float().contiguous()
         return ops.residual_rms_norm(residual, delta, self._scale32, self.eps, mult, then._scale32, then.eps)
 
     def as_rms_scale(self) -> tuple[torch.Tensor, float]:
