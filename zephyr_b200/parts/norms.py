@@ -30,6 +30,9 @@ class RMSNorm(Norm):
     def weight_decls(spec: NormSpec) -> dict[str, WeightDecl]:
         return {spec.weight: WeightDecl((spec.size,), ROLE_NORM)}
 
+    def weights_read(self) -> list[torch.Tensor]:
+        return [self.weight]          # (the float32 copy of the scales stands in for them, not beside them)
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if x.dtype == torch.float32 and self.dtype != torch.float32:
             return ops.sum_rms_norm(x, None, None, self.weight, self.eps, out_dtype=self.dtype)    # a float32 stream
