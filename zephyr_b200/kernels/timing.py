@@ -598,6 +598,129 @@ def head_linear(args) -> dict:
 CASES.update({"experts": experts, "head_linear": head_linear, "stream_parts": stream_parts})
 
 
+def delta_rule(args) -> dict:
+    """The gated delta rule (unit norms, steps and decays, then the scan): one request of ``--tokens`` tokens, or
+    ``--rows`` requests of one token each with ``--tokens 0``; ``--heads`` value heads on ``--kv-heads`` q/k heads of
+    ``--head-dim`` key channels and ``--value-dim`` value channels."""
+    device = torch.device("cuda")
+    heads, groups, D, V = args.heads, args.kv_heads, args.head_dim, args.value_dim
+    T, slots, starts, lens = _row_shape(args, device)
+    n = _copies(T * (2 * groups * D + heads * V) * 4)
+    q = [torch.randn((T, groups * D), device=device) for _ in range(n)]
+    k = [torch.randn((T, groups * D), device=device) for _ in range(n)]
+    v = [torch.randn((T, heads * V), device=device) for _ in range(n)]
+    steps = torch.randn((T, 2 * heads), device=device)
+    a_log, dt_bias = torch.zeros(heads, device=device) - 1.0, torch.zeros(heads, device=device)
+    state = torch.zeros((slots.numel(), heads * D * V), device=device)
+    status = ops.new_status(device)
+    us = _time(lambda i: ops.delta_rule(q[i % n], k[i % n], v[i % n], steps[:, :heads], steps[:, heads:], a_log, dt_bias, heads,
+                                        groups, D, V, state, slots, starts, lens, status, q_scale=D ** -0.5),
+               args.warmup, args.iters)
+    ops.check_status(status, "delta_rule")
+    per_token = 7.0 * heads * D * V          # three sums of D x V multiply-adds and the write, as operations
+    return {"tokens": T, "requests": slots.numel(), "heads": heads, "key_channels": D, "value_channels": V, "us": round(us, 2),
+            "tflops_f32": round(T * per_token / us / 1e6, 2),
+            "state_gbs": round(2 * slots.numel() * heads * D * V * 4 / us / 1e3, 1)}
+
+
+def windowed_attention(args) -> dict:
+    """Attention over a window of ``--window`` (default 1024) with the masks that come in runs of key tiles: pooled
+    blocks of 16 positions, 64 kept first tokens, and every head's weights on every key/value head's values; a
+    prompt of ``--tokens`` tokens as tiles of tokens, and ``--batch`` single tokens at ``--context`` as tiles of a
+    group's heads, on the mma.sync prompt kernel; beside them the window alone."""
+    device = torch.device("cuda")
+    H, G, d, page = args.heads, args.kv_heads, args.head_dim, args.page_size
+    window = args.window or 1024
+    status = ops.new_status(device)
+    out = {"heads": H, "kv_heads": G, "head_dim": d, "window": window}
+
+    def run(new_tokens: int, before: int, requests: int, pool=0, keep_first=0, cross=False) -> float:
+        T = new_tokens * requests
+        q = torch.randn((T, H * d), device=device, dtype=torch.bfloat16)
+        caches, table = _paged_inputs(requests, before + new_tokens, G, d, page, device)
+        pooled = torch.randn_like(caches[0])
+        start = torch.arange(0, T, new_tokens, dtype=torch.int32, device=device)
+        lens = torch.full((requests,), new_tokens, dtype=torch.int32, device=device)
+        ctx = torch.full((requests,), before, dtype=torch.int32, device=device)
+        single = new_tokens == 1
+        tile = 1 if single else ops.paged_prefill_tile_tokens()
+        per = -(-new_tokens // tile)
+        tile_row = torch.arange(requests, dtype=torch.int32, device=device).repeat_interleave(per)
+        tile_q0 = (torch.arange(per, dtype=torch.int32, device=device) * tile).repeat(requests)
+        result = torch.empty((T, H * d * (G if cross else 1)), device=device, dtype=torch.float32 if cross else torch.bfloat16)
+        extra = dict(pool=pool, pool_cache=pooled, pool_table=table) if pool else {}
+        masked = bool(pool or keep_first or cross)
+        return _time(lambda i: ops.paged_prefill(q, caches[i % len(caches)], table, tile_row, tile_q0, start, lens, ctx, H, G, d,
+                                                 window, d ** -0.5, status, result, keep_first=keep_first, cross_values=cross,
+                                                 by_group=single and masked and H // G <= 16, **extra),
+                     args.warmup, args.iters)
+
+    for name, masks in (("window alone", {}), ("blocks of 16", {"pool": 16}), ("64 kept", {"keep_first": 64}),
+                        ("64 kept, pairs of heads", {"keep_first": 64, "cross": True})):
+        out[name] = {"prompt_us": round(run(args.tokens, 0, 1, **masks), 1),
+                     "single_tokens_us": round(run(1, args.context - 1, args.batch, **masks), 1)}
+    ops.check_status(status, "windowed_attention")
+    return out
+
+
+def window_parts(args) -> dict:
+    """The small kernels around windowed attention, each beside its like where there is one: norms + rotation of
+    halves + cache write beside unit norms + cache write with keys as values; the means of blocks; the mixing of
+    heads; the sigmoid gate; the sum of an RMS-normed output into a float32 stream beside the layer-norm form;
+    routing by the largest biased logits beside softmax routing."""
+    device = torch.device("cuda")
+    T, W, H, G, d, page = args.tokens, args.hidden, args.heads, args.kv_heads, args.head_dim, args.page_size
+    bf = torch.bfloat16
+    status = ops.new_status(device)
+    out = {"tokens": T, "hidden": W}
+    n = _copies(T * W * 12)
+    stream = [torch.randn((T, W), device=device) for _ in range(n)]
+    delta = [torch.randn((T, W), device=device, dtype=bf) for _ in range(n)]
+    w = torch.ones(W, device=device)
+    us = _time(lambda i: ops.residual_rms_norm(stream[i % n], delta[i % n], w, 1e-6, 0.7, rounded_sum=True), args.warmup, args.iters)
+    out["residual_rms_norm_rounded_sum"] = {"us": round(us, 2), "gbs": round(T * W * 12 / us / 1e3, 1)}
+    us = _time(lambda i: ops.residual_layer_norm(stream[i % n], delta[i % n], w, None, 1e-6, 1.0, rounded_sum=True), args.warmup, args.iters)
+    out["like: residual_layer_norm_rounded_sum"] = {"us": round(us, 2), "gbs": round(T * W * 12 / us / 1e3, 1)}
+    blocks = -(-T // page)
+    table = torch.arange(1, blocks + 1, dtype=torch.int32, device=device).view(1, -1)
+    cache = torch.zeros((blocks + 1, 2, G, page, d), dtype=bf, device=device)
+    pooled = torch.zeros_like(cache)
+    positions = torch.arange(T, dtype=torch.int32, device=device)
+    rows = torch.zeros(T, dtype=torch.int32, device=device)
+    width = (H + 2 * G) * d
+    m = _copies(T * width * 4)
+    projected = [torch.randn((T, width), device=device) for _ in range(m)]
+    q_w, k_w, freqs = torch.ones(H * d, device=device), torch.ones(G * d, device=device), torch.rand(d // 4, device=device)
+    us = _time(lambda i: ops.qkv_halves(projected[i % m], H, G, d, d, "whole", q_w, k_w, 1e-6, freqs, d // 2, 1.0, True, positions,
+                                        rows, cache, table, status, bf), args.warmup, args.iters)
+    out["qkv_halves"] = {"us": round(us, 2), "gbs": round(T * width * 6 / us / 1e3, 1)}
+    narrow = (H + G) * d
+    us = _time(lambda i: ops.qkv_pairs(projected[i % m][:, :narrow], H, G, d, d, None, None, None, 1e-6, None, 0, positions, rows,
+                                       cache, table, status, bf, unit_norm=True, values_from_keys=True, q_temp=(0.2, 128)),
+               args.warmup, args.iters)
+    out["like: qkv_pairs_keys_as_values"] = {"us": round(us, 2), "gbs": round(T * (narrow * 4 + width * 2) / us / 1e3, 1)}
+    us = _time(lambda i: ops.pool_blocks(cache, table, pooled, table, positions, rows, G, d, d, 16, status), args.warmup, args.iters)
+    out["pool_blocks_of_16"] = {"us": round(us, 2), "read_mb": round(T * 2 * G * d * 2 / 1e6, 1)}
+    crossed = torch.randn((T, H * G * d), device=device)
+    mix = torch.randn((H, H), device=device)
+    us = _time(lambda i: ops.head_mix(crossed, mix, H, G, d, bf), args.warmup, args.iters)
+    out["head_mix"] = {"us": round(us, 2), "gbs": round((crossed.numel() * 4 + T * H * d * 2) / us / 1e3, 1)}
+    attended = torch.randn((T, H * d), device=device, dtype=bf)
+    gate = torch.randn((T, H * d), device=device)
+    us = _time(lambda i: ops.sigmoid_gate(attended, gate), args.warmup, args.iters)
+    out["sigmoid_gate"] = {"us": round(us, 2), "gbs": round(T * H * d * 8 / us / 1e3, 1)}
+    logits, bias = torch.randn((T, args.experts), device=device), torch.randn(args.experts, device=device)
+    us = _time(lambda i: ops.route(logits, None, args.top, "top_softmax", logit_bias=bias), args.warmup, args.iters)
+    out["route_top_softmax"] = {"us": round(us, 2)}
+    us = _time(lambda i: ops.route(logits, None, args.top, "softmax"), args.warmup, args.iters)
+    out["like: route_softmax"] = {"us": round(us, 2)}
+    ops.check_status(status, "window_parts")
+    return out
+
+
+CASES.update({"delta_rule": delta_rule, "windowed_attention": windowed_attention, "window_parts": window_parts})
+
+
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(prog="python -m zephyr_b200.kernels.timing", description=__doc__.split("\n")[0])
     parser.add_argument("case", choices=sorted(CASES))
