@@ -305,14 +305,14 @@ def build_rizovik_pair(size: str, batch: int, context: int):
     routed = {"kind": "moe", "expert": {"ff": z["ff"] // z["top"]}, "router": {"experts": z["experts"], "top": z["top"]}}
     sizes = dict(heads=z["heads"], kv_heads=z["kv_heads"], dim=hd, vdim=hd, scale=hd ** -0.5)
     pooled = {"type": "attention", "mlp": routed,
-              "mixer": dict(sizes, rot={"base": 250000.0, "dims": hd // 2}, mask={"size": z["window"], "pool": z["pool"]})}
+              "mixer": dict(sizes, rot={"base": 300000.0, "dims": hd // 2}, mask={"size": z["window"], "pool": z["pool"]})}
     kept = {"type": "attention_2", "mlp": routed,
-            "mixer": dict(sizes, rot={"base": 50000.0, "dims": hd // 4, "scaling": {"factor": 8.0}},
+            "mixer": dict(sizes, rot={"base": 40000.0, "dims": hd // 4, "scaling": {"factor": 4.0}},
                           mask={"size": z["window"], "keep_first": z["keep_first"]})}
     delta = {"type": "delta", "mlp": routed, "mixer": dict(conv=4, **z["delta"])}
     six = [pooled, kept, delta, pooled, kept, delta]
     layers = six + [dict(six[0], weights_of=0), dict(six[1], weights_of=1)]
-    rizovik = RizovikConfig(vocab=32768, width=z["width"], norm_eps=1e-6, residual_mult=0.7, layers=tuple(layers[:z["layers"]]))
+    rizovik = RizovikConfig(vocab=32768, width=z["width"], norm_eps=1e-6, residual_mult=0.6, layers=tuple(layers[:z["layers"]]))
     old_routed = {"kind": "moe", "expert": {"ff": z["ff"] // z["top"]}, "router": {"experts": z["experts"], "identity": 0, "top": z["top"]}}
     capped = dict(heads=z["heads"], kv_heads=z["kv_heads"], dim=hd, vdim=hd, scale=hd ** -0.5, softcap=50.0,
                   q_temp={"coef": 0.2, "every": 128})

@@ -62,7 +62,7 @@ def _a_layers():
 
 def _b_layers():
     layers = [delta(3, 1, 96, 70, 4, moe(7, 3, 50)),
-              pooled(8, 1, 32, 32, 40, 64, rot(250000.0, 32), 0.18, moe(9, 2, 64)),
+              pooled(8, 1, 32, 32, 36, 64, rot(300000.0, 32), 0.18, moe(9, 2, 72)),
               kept(5, 5, 16, 24, 70, 33, rot(1000.0, 6), 0.35, None),
               pooled(3, 3, 40, 8, 12, 12, rot(20.0, 40, factor=2.0), 0.22, moe(3, 2, 27))]
     return layers + [again(layers, 1)]
@@ -71,7 +71,7 @@ def _b_layers():
 CONFIGS = {
     # A: a block smaller than its window and than a page, kept tokens fewer than a page and none, groups of
     # two, value heads wider and narrower than the keys, delta heads of few channels, layers run twice
-    "A": model(97, 64, 0.7, 1e-5, _a_layers()),
+    "A": model(97, 64, 0.6, 1e-5, _a_layers()),
     # B: a block larger than its window and than a page (tokens leave the window before their block is whole),
     # a block as long as the window, more kept tokens than a page holds, a multiplier of one, delta heads of 96
     # channels with one q/k head for three value heads, pages of 32
@@ -79,11 +79,11 @@ CONFIGS = {
     # C: head sizes that the tensor-core kernels would take, 16 heads on 2, a window of one token, a block of
     # one token, eight taps and one tap
     "C": model(64, 128, 0.5, 1e-6, [
-        pooled(16, 2, 64, 64, 1, 1, rot(1000.0, 64), 0.125, moe(12, 2, 24)),
+        pooled(16, 2, 64, 64, 1, 1, rot(1000.0, 64), 0.125, moe(11, 2, 24)),
         delta(2, 2, 16, 128, 8, moe(2, 1, 48)),
-        kept(8, 4, 128, 128, 33, 40, rot(500000.0, 32, factor=8.0), 0.09, moe(4, 2, 16)),
+        kept(8, 4, 128, 128, 33, 40, rot(500000.0, 32, factor=16.0), 0.09, moe(4, 2, 16)),
         delta(6, 3, 128, 32, 1, None),
-        pooled(2, 1, 128, 128, 50, 16, rot(100.0, 2), 0.1, moe(8, 3, 40))]),
+        pooled(2, 1, 128, 128, 50, 14, rot(100.0, 2), 0.1, moe(8, 3, 40))]),
 }
 PAGE_SIZE = {"A": 16, "B": 32, "C": 16}
 

@@ -52,9 +52,9 @@ def test_the_spec_names_every_mechanism_with_its_constants():
     assert stores[4] == PagedCacheSpec(2, key_dim=48, window=9)
     assert stores[3] == stores[7] == StateCacheSpec((4 * 24 * 20 + 2 * (2 * 2 * 24 + 4 * 20),), "float32")
     wide = RizovikConfig.from_dict(CONFIGS["B"]).to_model_spec()
-    assert cache_specs(wide)[1].window == 64 and wide.layers[1].mixer.params["window"] == 40     # a block longer than the window
+    assert cache_specs(wide)[1].window == 64 and wide.layers[1].mixer.params["window"] == 36     # a block longer than the window
     assert [layer.block for layer in spec.layers] == ["outnorm_residual"] * 4
-    assert all(layer.block_params == {"residual_mult": 0.7} for layer in spec.layers)
+    assert all(layer.block_params == {"residual_mult": 0.6} for layer in spec.layers)
     assert all(norm.kind == "rmsnorm" for layer in spec.layers for norm in layer.norms.values())
     assert spec.output.params["weight"] == "embed"                              # the head is the table itself
     first, second, third = (spec.layers[i].mixer for i in range(3))

@@ -30,9 +30,9 @@ CLOSE_CALL = {"float32": 2e-4, "bfloat16": 0.05}
 
 ONE_LAYER = {
     # single layers: the mechanism alone, through the engine
-    "pooled": model(50, 48, 0.7, 1e-6, [pooled(3, 1, 16, 24, 11, 4, rot(40.0, 12), 0.3, None)]),
+    "pooled": model(50, 48, 0.8, 1e-6, [pooled(3, 1, 16, 24, 11, 4, rot(40.0, 12), 0.3, None)]),
     "kept": model(50, 40, 1.3, 1e-6, [kept(4, 2, 12, 20, 13, 5, rot(90.0, 12, factor=3.0), 0.4, None)]),
-    "delta": model(50, 56, 0.7, 1e-5, [delta(2, 1, 40, 36, 4, None)]),
+    "delta": model(50, 56, 0.6, 1e-5, [delta(2, 1, 40, 36, 4, None)]),
     "routed": model(50, 40, 0.9, 1e-6, [delta(1, 1, 8, 8, 2, moe(10, 2, 24)), kept(2, 1, 8, 8, 4, 2, rot(10.0, 8), 0.5, moe(3, 1, 13))]),
 }
 ALL = {**CONFIGS, **ONE_LAYER}

@@ -115,8 +115,8 @@ def _expected_attention(dtype, q, k, v, H, G, visible_tokens, visible_blocks=Non
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H,G,d,dv,size,pool,page", [(4, 2, 32, 32, 40, 16, 16), (3, 1, 24, 40, 19, 5, 16), (8, 1, 64, 16, 12, 12, 32),
-                                                    (2, 2, 16, 48, 40, 64, 16), (6, 3, 128, 128, 70, 8, 64), (5, 1, 20, 20, 1, 1, 16),
+@pytest.mark.parametrize("H,G,d,dv,size,pool,page", [(4, 2, 32, 32, 44, 12, 16), (3, 1, 24, 40, 19, 5, 16), (8, 1, 64, 16, 12, 12, 32),
+                                                    (2, 2, 16, 48, 36, 64, 16), (6, 3, 128, 128, 70, 8, 64), (5, 1, 20, 20, 1, 1, 16),
                                                     (17, 1, 16, 16, 33, 3, 16), (4, 2, 64, 64, 19, 5, 16), (6, 1, 96, 96, 100, 2, 32),
                                                     (2, 1, 256, 256, 64, 64, 16)])
 def test_a_window_followed_by_pooled_blocks(cuda_device, dtype, H, G, d, dv, size, pool, page):
@@ -150,7 +150,7 @@ def test_a_window_followed_by_pooled_blocks(cuda_device, dtype, H, G, d, dv, siz
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H,G,d,dv,size,keep,page", [(4, 2, 32, 32, 96, 20, 16), (6, 3, 20, 12, 23, 7, 16), (2, 2, 48, 48, 9, 0, 16),
+@pytest.mark.parametrize("H,G,d,dv,size,keep,page", [(4, 2, 32, 32, 90, 22, 16), (6, 3, 20, 12, 23, 7, 16), (2, 2, 48, 48, 9, 0, 16),
                                                     (5, 5, 16, 24, 70, 33, 32), (8, 4, 128, 128, 33, 40, 16), (3, 1, 64, 64, 5, 1, 64),
                                                     (4, 1, 16, 16, 300, 4, 16), (6, 2, 32, 32, 70, 65, 16), (4, 4, 160, 160, 64, 64, 32)])
 def test_a_window_that_keeps_the_first_tokens_with_mixed_heads(cuda_device, dtype, H, G, d, dv, size, keep, page):
@@ -186,7 +186,7 @@ def test_a_window_that_keeps_the_first_tokens_with_mixed_heads(cuda_device, dtyp
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("H,G,d,dv,norm,scales,dims,factor,value_norm", [
     (4, 2, 32, 32, "whole", True, 16, None, True), (3, 1, 24, 40, "per_head", True, 24, 4.0, False),
-    (6, 6, 20, 12, "whole", False, 2, None, False), (2, 1, 128, 64, "per_head", False, 64, 8.0, True),
+    (6, 6, 20, 12, "whole", False, 2, None, False), (2, 1, 128, 64, "per_head", False, 64, 16.0, True),
     (5, 1, 16, 16, "none", False, 16, None, True), (8, 2, 64, 64, "whole", True, 0, None, True)])
 def test_norms_rotation_of_halves_and_the_cache_write(cuda_device, dtype, H, G, d, dv, norm, scales, dims, factor, value_norm):
     """Queries that come out of the kernel and, through an attention over one key per query (a window of one
@@ -222,7 +222,7 @@ def test_norms_rotation_of_halves_and_the_cache_write(cuda_device, dtype, H, G, 
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("heads,groups,dim,vdim", [(2, 1, 32, 64), (4, 2, 24, 20), (3, 1, 96, 70), (6, 3, 128, 32), (2, 2, 16, 128),
+@pytest.mark.parametrize("heads,groups,dim,vdim", [(2, 1, 32, 48), (4, 2, 24, 20), (3, 1, 96, 70), (6, 3, 128, 32), (2, 2, 16, 128),
                                                    (1, 1, 200, 9), (8, 2, 8, 20), (2, 1, 64, 64), (3, 3, 40, 36)])
 def test_the_delta_rule_in_portions_over_slots_used_again(cuda_device, dtype, heads, groups, dim, vdim):
     """Two requests side by side in portions of unequal sizes (down to one and two tokens), then a third in the
@@ -323,7 +323,7 @@ def test_the_sum_of_a_normed_output_into_the_stream(cuda_device, dtype, width):
     from zephyr_b200.kernels import ops
 
     g = torch.Generator().manual_seed(width)
-    rows, mult, eps = 37, 0.7, 1e-5
+    rows, mult, eps = 37, 0.6, 1e-5
     stream = torch.randn(rows, width, generator=g) * 3.0
     delta_rows = (torch.randn(rows, width, generator=g) * 0.01).to(DTYPES[dtype])
     w1, w2 = torch.randn(width, generator=g) * 0.2 + 1.0, torch.randn(width, generator=g) * 0.2 + 1.0

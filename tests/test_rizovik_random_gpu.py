@@ -28,7 +28,7 @@ def draw_config(seed: int) -> dict:
 
     def rotation(dim):
         dims = rng.choice([d for d in (2, 4, 6, 8, 16, 20, 32, 64, 128, dim) if d <= dim and d % 2 == 0])
-        return rot(rng.choice([20.0, 500.0, 10000.0, 250000.0]), dims, rng.choice([None, None, 1.0, 2.0, 8.0]))
+        return rot(rng.choice([20.0, 500.0, 10000.0, 300000.0]), dims, rng.choice([None, None, 1.0, 2.0, 16.0]))
 
     def heads():
         groups = rng.choice([1, 1, 2, 3, 4])
@@ -53,7 +53,7 @@ def draw_config(seed: int) -> dict:
     layers = [layer() for _ in range(rng.randint(1, 5))]
     for _ in range(rng.choice([0, 0, 1, 2])):
         layers.append(again(layers, rng.randrange(len([l for l in layers if "weights_of" not in l]))))
-    return model(rng.randint(50, 700), width, rng.choice([0.5, 0.7, 1.0, 1.4]), rng.choice([1e-5, 1e-6]), layers)
+    return model(rng.randint(50, 700), width, rng.choice([0.5, 0.8, 1.0, 1.4]), rng.choice([1e-5, 1e-6]), layers)
 
 
 @pytest.mark.parametrize("seed,dtype", [(s, "float32") for s in list(range(12)) + list(range(100, 108))] + [(s, "bfloat16") for s in range(100, 108)])
