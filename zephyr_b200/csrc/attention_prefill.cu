@@ -176,6 +176,7 @@ paged_prefill_kernel(const PrefillArgs a) {
   // Pooled entries in sight of this lane's two rows, and of the warp's last row: worked out once, not per score.
   const int seen[2] = {a.pool > 0 ? (qpos[0] - a.window + 1) / a.pool : 0, a.pool > 0 ? (qpos[1] - a.window + 1) / a.pool : 0};
   const int warp_seen = a.pool > 0 ? (warp_last_pos - a.window + 1) / a.pool : 0;
+  const int warp_seen_first = a.pool > 0 ? (warp_pos0 - a.window + 1) / a.pool : 0;      // what the warp's first row sees
 
   unsigned qa[HD / 16][4];
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
@@ -219,22 +220,39 @@ paged_prefill_kernel(const PrefillArgs a) {
     }
 
     float tile_max[2] = {-INFINITY, -INFINITY};
+    // A tile that every row of the warp sees whole needs no mask: most tiles of a long window are such.
+    const bool whole_tile =
+        run == 0 ? k0 + PRE_BN <= warp_seen_first
+      : run == 1 ? k0 + PRE_BN <= kept
+                 : k0 + PRE_BN - 1 <= warp_pos0 && k0 >= lo && (a.window == 0 || k0 > warp_last_pos - a.window) &&
+                       (a.chunk == 0 || k0 >= warp_last_pos / a.chunk * a.chunk);
+    if (whole_tile) {
 #pragma unroll
-    for (int i = 0; i < NTS; ++i) {
-      const int nt = DEC ? warp : i;
+      for (int i = 0; i < NTS; ++i) {
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const int pos = k0 + nt * 8 + quad_col + (c & 1);
-        const int qp = qpos[c >> 1];
-        const bool valid = run == 0 ? pos < seen[c >> 1]
-                         : run == 1 ? pos < kept
-                                    : pos <= qp && pos >= lo &&
-                                          (a.window == 0 || pos > qp - a.window || pos < a.keep_first) &&
-                                          pos >= chunk_start[c >> 1];
-        const float scaled = a.softcap_log2 > 0.0f ? a.softcap_log2 * tanhf(s[i][c] * a.scale_over_cap)
-                                                   : s[i][c] * a.scale_log2;
-        s[i][c] = valid ? scaled : -INFINITY;
-        tile_max[c >> 1] = fmaxf(tile_max[c >> 1], s[i][c]);
+        for (int c = 0; c < 4; ++c) {
+          s[i][c] = a.softcap_log2 > 0.0f ? a.softcap_log2 * tanhf(s[i][c] * a.scale_over_cap) : s[i][c] * a.scale_log2;
+          tile_max[c >> 1] = fmaxf(tile_max[c >> 1], s[i][c]);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < NTS; ++i) {
+        const int nt = DEC ? warp : i;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int pos = k0 + nt * 8 + quad_col + (c & 1);
+          const int qp = qpos[c >> 1];
+          const bool valid = run == 0 ? pos < seen[c >> 1]
+                           : run == 1 ? pos < kept
+                                      : pos <= qp && pos >= lo &&
+                                            (a.window == 0 || pos > qp - a.window || pos < a.keep_first) &&
+                                            pos >= chunk_start[c >> 1];
+          const float scaled = a.softcap_log2 > 0.0f ? a.softcap_log2 * tanhf(s[i][c] * a.scale_over_cap)
+                                                     : s[i][c] * a.scale_log2;
+          s[i][c] = valid ? scaled : -INFINITY;
+          tile_max[c >> 1] = fmaxf(tile_max[c >> 1], s[i][c]);
+        }
       }
     }
     float corr[2], m_use[2];
