@@ -75,9 +75,9 @@ def _run_attention(cuda_device, dtype, q, k, v, H, G, page, portions, *, window,
             wide_q0 = torch.arange(0, n, ops.paged_prefill_tile_tokens(), dtype=torch.int32, device=cuda_device)
             out = torch.full((n, H * dv * (G if mix is not None else 1)), float("nan"), device=cuda_device,
                              dtype=torch.float32 if mix is not None else torch_dtype)
-            # (a single token's query rows are the heads of a group)
+            # (a single token's query rows are the heads of a group, where a group has at most 16)
             ops.paged_prefill(qs, cache, table, torch.zeros_like(wide_q0), wide_q0, *rows, H, G, d, window, scale, status, out,
-                              keep_first=keep_first, cross_values=mix is not None, by_group=n == 1, **extra)
+                              keep_first=keep_first, cross_values=mix is not None, by_group=n == 1 and H // G <= 16, **extra)
             outs.append(ops.head_mix(out, mix.float().to(cuda_device), H, G, dv, torch_dtype) if mix is not None else out)
         elif mix is not None:
             crossed = ops.paged_attention(*args, value_dim=dv, keep_first=keep_first, cross_values=True,
@@ -118,7 +118,7 @@ def _expected_attention(dtype, q, k, v, H, G, visible_tokens, visible_blocks=Non
 @pytest.mark.parametrize("H,G,d,dv,size,pool,page", [(4, 2, 32, 32, 44, 12, 16), (3, 1, 24, 40, 19, 5, 16), (8, 1, 64, 16, 12, 12, 32),
                                                     (2, 2, 16, 48, 36, 64, 16), (6, 3, 128, 128, 70, 8, 64), (5, 1, 20, 20, 1, 1, 16),
                                                     (17, 1, 16, 16, 33, 3, 16), (4, 2, 64, 64, 19, 5, 16), (6, 1, 96, 96, 100, 2, 32),
-                                                    (2, 1, 256, 256, 64, 64, 16)])
+                                                    (2, 1, 256, 256, 64, 64, 16), (34, 2, 32, 32, 21, 3, 16)])
 def test_a_window_followed_by_pooled_blocks(cuda_device, dtype, H, G, d, dv, size, pool, page):
     """Queries of head 0 point at the last key inside the window, at the first one outside it (which may be
     seen only through its block's mean, or not at all), at a key of the block that has just come into sight, at
@@ -152,7 +152,8 @@ def test_a_window_followed_by_pooled_blocks(cuda_device, dtype, H, G, d, dv, siz
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("H,G,d,dv,size,keep,page", [(4, 2, 32, 32, 90, 22, 16), (6, 3, 20, 12, 23, 7, 16), (2, 2, 48, 48, 9, 0, 16),
                                                     (5, 5, 16, 24, 70, 33, 32), (8, 4, 128, 128, 33, 40, 16), (3, 1, 64, 64, 5, 1, 64),
-                                                    (4, 1, 16, 16, 300, 4, 16), (6, 2, 32, 32, 70, 65, 16), (4, 4, 160, 160, 64, 64, 32)])
+                                                    (4, 1, 16, 16, 300, 4, 16), (6, 2, 32, 32, 70, 65, 16), (4, 4, 160, 160, 64, 64, 32),
+                                                    (17, 1, 64, 64, 30, 9, 16)])
 def test_a_window_that_keeps_the_first_tokens_with_mixed_heads(cuda_device, dtype, H, G, d, dv, size, keep, page):
     """Queries of head 0 point at the last kept token, the first one that is not kept, the edges of the window
     and the first token; the heads' weights are mixed by a matrix with entries of both signs, so every head's
