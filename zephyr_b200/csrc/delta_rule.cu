@@ -97,11 +97,14 @@ struct DeltaScanArgs {
 // the NEXT token's k and q in registers while the chain S -> S^T k -> u -> S of the present token runs, and
 // sums its products in four separate sums, so the chain a token adds is the reduction over the L lanes, one
 // multiply-add and the write, not the loads.  k . q is summed over the same lanes beside the two read-outs.
-template <typename T, int KPL, int L, bool ASYNC>
+// CPT: value columns a thread holds (its group's column and the one `groups` further on): two columns are two
+// chains whose waits overlap; a step of single tokens keeps one, so that its CTAs stay many.
+template <typename T, int KPL, int L, int CPT, bool ASYNC>
 __global__ void __launch_bounds__(DS_THREADS) delta_scan_kernel(const DeltaScanArgs a) {
   extern __shared__ __align__(16) float ds_smem[];
   constexpr int RUN = KPL + 4, DP = L * RUN;      // a lane's run and a token's row in shared memory
-  constexpr int cols = DS_THREADS / L;            // value columns of this CTA
+  constexpr int groups = DS_THREADS / L;          // groups of L lanes
+  constexpr int cols = groups * CPT;              // value columns of this CTA: CPT a group (column group + c * groups)
   constexpr int stage_floats = 2 * DS_TOKENS * DP + DS_TOKENS * cols + 2 * DS_TOKENS;
   // one stage: q [DS_TOKENS][DP], k [DS_TOKENS][DP], v [DS_TOKENS][cols], beta [DS_TOKENS], decay [DS_TOKENS]
   const int D = a.D, V = a.V;
@@ -113,23 +116,30 @@ __global__ void __launch_bounds__(DS_THREADS) delta_scan_kernel(const DeltaScanA
     return;
   }
   const int t0 = a.row_q_start[row], n = a.row_q_len[row];
-  const int l = threadIdx.x % L, my_col = threadIdx.x / L, col = col0 + my_col;
-  const bool live = col < V;
+  const int l = threadIdx.x % L, my_group = threadIdx.x / L;
   const int group = head / a.heads_per_group, qk_heads = a.heads / a.heads_per_group;
-  float* mine = a.state + static_cast<long long>(slot) * a.slot_stride +
-                (static_cast<long long>(head) * V + (live ? col : 0)) * D + l * KPL;
-  const bool state_vectors = ASYNC && reinterpret_cast<uintptr_t>(mine) % 16 == 0;
-  float S[KPL];
-  if (state_vectors) {
+  // A thread's CPT columns are separate chains: one column's exchanges and writes run under the other's sums.
+  bool live[CPT];
+  float* mine[CPT];
+  float S[CPT][KPL];
+  const bool state_vectors = ASYNC && D % 4 == 0;
 #pragma unroll
-    for (int i = 0; i < KPL; i += 4) {
-      float4 x = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-      if (live && l * KPL + i < D) x = *reinterpret_cast<const float4*>(mine + i);
-      S[i] = x.x; S[i + 1] = x.y; S[i + 2] = x.z; S[i + 3] = x.w;
+  for (int c = 0; c < CPT; ++c) {
+    const int col = col0 + my_group + c * groups;
+    live[c] = col < V;
+    mine[c] = a.state + static_cast<long long>(slot) * a.slot_stride +
+              (static_cast<long long>(head) * V + (live[c] ? col : 0)) * D + l * KPL;
+    if (state_vectors) {
+#pragma unroll
+      for (int i = 0; i < KPL; i += 4) {
+        float4 x = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (live[c] && l * KPL + i < D) x = *reinterpret_cast<const float4*>(mine[c] + i);
+        S[c][i] = x.x; S[c][i + 1] = x.y; S[c][i + 2] = x.z; S[c][i + 3] = x.w;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < KPL; ++i) S[c][i] = (live[c] && l * KPL + i < D) ? mine[c][i] : 0.0f;
     }
-  } else {
-#pragma unroll
-    for (int i = 0; i < KPL; ++i) S[i] = (live && l * KPL + i < D) ? mine[i] : 0.0f;
   }
   for (int e = threadIdx.x; e < 2 * stage_floats; e += DS_THREADS) ds_smem[e] = 0.0f;
   __syncthreads();
@@ -196,29 +206,42 @@ __global__ void __launch_bounds__(DS_THREADS) delta_scan_kernel(const DeltaScanA
       x[i] = r.x; x[i + 1] = r.y; x[i + 2] = r.z; x[i + 3] = r.w;
     }
   };
-  float* out = a.out + static_cast<long long>(t0) * a.heads * V + head * V + col;
+  float* out = a.out + static_cast<long long>(t0) * a.heads * V + head * V + col0 + my_group;
   const long long out_stride = static_cast<long long>(a.heads) * V;
-  // One token: the read-outs of the old state, the write, the output.
-  auto token = [&](const float (&kr)[KPL], const float (&qr)[KPL], float g, float beta, float vj, long long at) {
-    float rk[4] = {0.0f, 0.0f, 0.0f, 0.0f}, rq[4] = {0.0f, 0.0f, 0.0f, 0.0f}, kq[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  // One token: the read-outs of the old state, the write, the output, for each of the thread's columns.
+  auto token = [&](const float (&kr)[KPL], const float (&qr)[KPL], float g, float beta, const float* vj, long long at) {
+    float kq[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-    for (int i = 0; i < KPL; ++i) {
-      rk[i & 3] = fmaf(S[i], kr[i], rk[i & 3]);
-      rq[i & 3] = fmaf(S[i], qr[i], rq[i & 3]);
-      kq[i & 3] = fmaf(kr[i], qr[i], kq[i & 3]);
-    }
-    float sk = (rk[0] + rk[1]) + (rk[2] + rk[3]), sq = (rq[0] + rq[1]) + (rq[2] + rq[3]);
+    for (int i = 0; i < KPL; ++i) kq[i & 3] = fmaf(kr[i], qr[i], kq[i & 3]);
     float skq = (kq[0] + kq[1]) + (kq[2] + kq[3]);
+    float sk[CPT], sq[CPT];
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) {
+      float rk[4] = {0.0f, 0.0f, 0.0f, 0.0f}, rq[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+      for (int i = 0; i < KPL; ++i) {
+        rk[i & 3] = fmaf(S[c][i], kr[i], rk[i & 3]);
+        rq[i & 3] = fmaf(S[c][i], qr[i], rq[i & 3]);
+      }
+      sk[c] = (rk[0] + rk[1]) + (rk[2] + rk[3]);
+      sq[c] = (rq[0] + rq[1]) + (rq[2] + rq[3]);
+    }
 #pragma unroll
     for (int o = L >> 1; o > 0; o >>= 1) {
-      sk += __shfl_xor_sync(0xffffffffu, sk, o);
-      sq += __shfl_xor_sync(0xffffffffu, sq, o);
       skq += __shfl_xor_sync(0xffffffffu, skq, o);
-    }
-    const float u = beta * (vj - g * sk);
 #pragma unroll
-    for (int i = 0; i < KPL; ++i) S[i] = fmaf(kr[i], u, g * S[i]);
-    if (l == 0 && live) out[at * out_stride] = fmaf(u, skq, g * sq);
+      for (int c = 0; c < CPT; ++c) {
+        sk[c] += __shfl_xor_sync(0xffffffffu, sk[c], o);
+        sq[c] += __shfl_xor_sync(0xffffffffu, sq[c], o);
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) {
+      const float u = beta * (vj[c * groups] - g * sk[c]);
+#pragma unroll
+      for (int i = 0; i < KPL; ++i) S[c][i] = fmaf(kr[i], u, g * S[c][i]);
+      if (l == 0 && live[c]) out[at * out_stride + c * groups] = fmaf(u, skq, g * sq[c]);
+    }
   };
 
   if (chunks > 0) {
@@ -239,7 +262,7 @@ __global__ void __launch_bounds__(DS_THREADS) delta_scan_kernel(const DeltaScanA
     }
     const float* q_s = stage + l * RUN;
     const float* k_s = stage + DS_TOKENS * DP + l * RUN;
-    const float* v_s = stage + 2 * DS_TOKENS * DP + my_col;
+    const float* v_s = stage + 2 * DS_TOKENS * DP + my_group;
     const float* beta_s = stage + 2 * DS_TOKENS * DP + DS_TOKENS * cols;
     const float* decay_s = beta_s + DS_TOKENS;
     // Tokens in pairs: while one token's chain runs on one set of registers, the next token's k and q are
@@ -251,24 +274,27 @@ __global__ void __launch_bounds__(DS_THREADS) delta_scan_kernel(const DeltaScanA
       const int j1 = j + 1 < DS_TOKENS ? j + 1 : j, j2 = j + 2 < DS_TOKENS ? j + 2 : j;
       load_run(k1, k_s + j1 * DP);
       load_run(q1, q_s + j1 * DP);
-      token(k0, q0, decay_s[j], beta_s[j], v_s[j * cols], base + j);
+      token(k0, q0, decay_s[j], beta_s[j], v_s + j * cols, base + j);
       if (j + 1 >= nt) break;
       load_run(k0, k_s + j2 * DP);
       load_run(q0, q_s + j2 * DP);
-      token(k1, q1, decay_s[j + 1], beta_s[j + 1], v_s[(j + 1) * cols], base + j + 1);
+      token(k1, q1, decay_s[j + 1], beta_s[j + 1], v_s + (j + 1) * cols, base + j + 1);
     }
     if (more) store_rest(other);
   }
   cp_async_wait<0>();
-  if (a.write_state && live) {
+#pragma unroll
+  for (int c = 0; c < CPT; ++c) {
+    if (!a.write_state || !live[c]) continue;
     if (state_vectors) {
 #pragma unroll
       for (int i = 0; i < KPL; i += 4)
-        if (l * KPL + i < D) *reinterpret_cast<float4*>(mine + i) = make_float4(S[i], S[i + 1], S[i + 2], S[i + 3]);
+        if (l * KPL + i < D)
+          *reinterpret_cast<float4*>(mine[c] + i) = make_float4(S[c][i], S[c][i + 1], S[c][i + 2], S[c][i + 3]);
     } else {
 #pragma unroll
       for (int i = 0; i < KPL; ++i)
-        if (l * KPL + i < D) mine[i] = S[i];
+        if (l * KPL + i < D) mine[c][i] = S[c][i];
     }
   }
 }
@@ -295,13 +321,13 @@ ZB_API int zb_delta_gates(float* q_out, float* k_out, float* beta, float* decay,
   return launch_result();
 }
 
-template <typename T, int KPL, int L>
+template <typename T, int KPL, int L, int CPT>
 static int delta_scan_launch(const DeltaScanArgs& a, int rows, cudaStream_t s) {
-  constexpr int cols = DS_THREADS / L;
+  constexpr int cols = DS_THREADS / L * CPT;
   const size_t smem = 2 * sizeof(float) * (2 * DS_TOKENS * L * (KPL + 4) + DS_TOKENS * cols + 2 * DS_TOKENS);
   const bool async = a.D % 4 == 0 && reinterpret_cast<uintptr_t>(a.q) % 16 == 0 && reinterpret_cast<uintptr_t>(a.k) % 16 == 0 &&
                      reinterpret_cast<uintptr_t>(a.state) % 16 == 0 && a.slot_stride % 4 == 0;
-  auto kernel = async ? delta_scan_kernel<T, KPL, L, true> : delta_scan_kernel<T, KPL, L, false>;
+  auto kernel = async ? delta_scan_kernel<T, KPL, L, CPT, true> : delta_scan_kernel<T, KPL, L, CPT, false>;
   if (smem > 48 * 1024 &&
       cuda_failed(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem))))
     return ERR_CUDA;
@@ -309,23 +335,32 @@ static int delta_scan_launch(const DeltaScanArgs& a, int rows, cudaStream_t s) {
   return launch_result();
 }
 
+template <typename T, int KPL, int L>
+static int delta_scan_columns(const DeltaScanArgs& a, int rows, int tokens, cudaStream_t s) {
+  // Two columns a thread where requests bring runs of tokens (the chains hide each other's waits) and a head has
+  // columns enough; one where a step is single tokens, whose time is the state's bytes.
+  const bool runs = tokens >= 4 * rows && a.V >= 2 * (DS_THREADS / L);
+  return runs ? delta_scan_launch<T, KPL, L, 2>(a, rows, s) : delta_scan_launch<T, KPL, L, 1>(a, rows, s);
+}
+
 template <typename T>
-static int delta_scan_dispatch(const DeltaScanArgs& a, int rows, cudaStream_t s) {
+static int delta_scan_dispatch(const DeltaScanArgs& a, int rows, int tokens, cudaStream_t s) {
   // Channels a lane holds and lanes a column: a column spreads over 4 lanes up to 64 channels (two rounds of
   // exchanges a token), over 8 up to 128, 16 up to 256, a whole warp beyond.
   const int D = a.D;
-  if (D <= 16) return delta_scan_launch<T, 4, 4>(a, rows, s);
-  if (D <= 32) return delta_scan_launch<T, 8, 4>(a, rows, s);
-  if (D <= 64) return delta_scan_launch<T, 16, 4>(a, rows, s);
-  if (D <= 128) return delta_scan_launch<T, 16, 8>(a, rows, s);
-  if (D <= 256) return delta_scan_launch<T, 16, 16>(a, rows, s);
-  return delta_scan_launch<T, 16, 32>(a, rows, s);
+  if (D <= 16) return delta_scan_columns<T, 4, 4>(a, rows, tokens, s);
+  if (D <= 32) return delta_scan_columns<T, 8, 4>(a, rows, tokens, s);
+  if (D <= 64) return delta_scan_columns<T, 16, 4>(a, rows, tokens, s);
+  if (D <= 128) return delta_scan_columns<T, 16, 8>(a, rows, tokens, s);
+  if (D <= 256) return delta_scan_columns<T, 16, 16>(a, rows, tokens, s);
+  return delta_scan_columns<T, 16, 32>(a, rows, tokens, s);
 }
 
 ZB_API int zb_delta_scan(float* out, const float* q, const float* k, const void* v, long long v_stride,
                          const float* beta, const float* decay, float* state, long long slot_stride, const int* slots,
-                         const int* row_q_start, const int* row_q_len, int rows, int heads, int heads_per_group, int D,
-                         int V, int num_slots, int write_state, int dtype, int* status, void* stream) {
+                         const int* row_q_start, const int* row_q_len, int rows, int tokens, int heads,
+                         int heads_per_group, int D, int V, int num_slots, int write_state, int dtype, int* status,
+                         void* stream) {
   if (rows < 0 || heads <= 0 || heads_per_group <= 0 || heads % heads_per_group != 0 || D <= 0 || V <= 0)
     return ERR_BAD_ARGUMENT;
   if (D > zb_delta_max_channels()) return ERR_UNSUPPORTED;
@@ -336,5 +371,6 @@ ZB_API int zb_delta_scan(float* out, const float* q, const float* k, const void*
   a.heads = heads; a.heads_per_group = heads_per_group; a.D = D; a.V = V; a.num_slots = num_slots;
   a.write_state = write_state; a.status = status;
   auto s = static_cast<cudaStream_t>(stream);
-  return dtype == DTYPE_F32 ? delta_scan_dispatch<float>(a, rows, s) : delta_scan_dispatch<__nv_bfloat16>(a, rows, s);
+  return dtype == DTYPE_F32 ? delta_scan_dispatch<float>(a, rows, tokens, s)
+                            : delta_scan_dispatch<__nv_bfloat16>(a, rows, tokens, s);
 }

@@ -110,8 +110,8 @@ _SIGNATURES = {
                        c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_int,
                        c_void_p],
     "zb_delta_scan": [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_longlong,
-                      c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
-                      c_void_p],
+                      c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                      c_void_p, c_void_p],
     "zb_residual_rms_norm": [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_float, c_float, c_int,
                              c_int, c_int, c_void_p],
     "zb_route_biased": [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -1031,7 +1031,7 @@ def delta_rule(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, b: torch.Tenso
                                     float(q_scale), float(unit_eps), DTYPE_CODE[v.dtype], _stream()), "delta_gates")
     out = torch.empty((T, heads * value_dim), dtype=torch.float32, device=dev)
     _check(library().zb_delta_scan(_ptr(out), _ptr(qn), _ptr(kn), _ptr(v), v.stride(0), _ptr(beta), _ptr(decay), _ptr(state),
-                                   state.stride(0), _ptr(slots), _ptr(row_q_start), _ptr(row_q_len), slots.numel(), heads,
+                                   state.stride(0), _ptr(slots), _ptr(row_q_start), _ptr(row_q_len), slots.numel(), T, heads,
                                    heads // qk_heads, key_dim, value_dim, state.shape[0], int(write_state),
                                    DTYPE_CODE[v.dtype], _ptr(status), _stream()), "delta_scan")
     return out
